@@ -32,6 +32,7 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: int = 0          # 0: every key is kept; n: only the last n keys are read
+    values: bool = True      # False: one vector per token only (a latent that serves as key and value)
 
 
 @dataclass(frozen=True)
@@ -63,10 +64,10 @@ class CacheGroup:
         self.seq_pages: dict[int, dict[int, int]] = {}      # slot -> {page index in sequence: page}
         self.dirty: set[int] = set()
         shape = (len(sites), n_pages, page_size, need.n_kv_heads, need.head_dim)
-        self.bytes = 2 * int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        self.bytes = (2 if need.values else 1) * int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
         # `alloc(shape, dtype)` hands out zeroed device memory, or None when only sizes are wanted
         self.k = alloc(shape, dtype)
-        self.v = alloc(shape, dtype)
+        self.v = alloc(shape, dtype) if need.values else None
         self.table_dev = alloc((n_slots, max_pages), torch.int32)
 
     def grow(self, slot: int, old_len: int, new_len: int) -> None:
@@ -264,14 +265,16 @@ class SequenceCache:
             if free:
                 idx = torch.as_tensor(free, dtype=torch.long, device=g.k.device)
                 g.k.index_fill_(1, idx, value)
-                g.v.index_fill_(1, idx, value)
+                if g.v is not None:
+                    g.v.index_fill_(1, idx, value)
             for slot, have in g.seq_pages.items():
                 length = self.lengths.get(slot, 0)
                 for p, page in have.items():
                     first = max(0, length - p * self.page_size)
                     if first < self.page_size:
                         g.k[:, page, first:] = value
-                        g.v[:, page, first:] = value
+                        if g.v is not None:
+                            g.v[:, page, first:] = value
 
     def check(self) -> None:
         """Invariants: no slot or page lost, held twice, or owned by two sequences."""

@@ -22,9 +22,10 @@ def architecture_name(raw: dict) -> str:
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs:
         return archs[0]
-    if isinstance(raw.get("model_type"), str):
-        return raw["model_type"]
-    raise ConfigError("config.json names no architecture (`architectures` or `model_type`)")
+    for key in ("architecture", "model_type"):
+        if isinstance(raw.get(key), str):
+            return raw[key]
+    raise ConfigError("config.json names no architecture (`architectures`, `architecture` or `model_type`)")
 
 
 def load_config(model_dir_or_dict):
@@ -36,6 +37,8 @@ def load_config(model_dir_or_dict):
 
 
 from . import llama_arch  # noqa: E402,F401  registers the Llama architecture
+from . import gevonex_arch  # noqa: E402,F401  registers the Gevonex architecture
+from .gevonex import GevonexConfig  # noqa: E402
 
-__all__ = ["Architecture", "ConfigError", "LlamaConfig", "RopeScaling", "RegistryError",
+__all__ = ["Architecture", "ConfigError", "GevonexConfig", "LlamaConfig", "RopeScaling", "RegistryError",
            "architecture_name", "load_config", "read_config_json"]

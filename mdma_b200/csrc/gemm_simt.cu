@@ -13,6 +13,7 @@ enum GemmMode : int {
     kStore = 0,        // out = acc
     kAccumulate = 1,   // out += acc        (the residual stream, float)
     kSwiGLU = 2,       // out = act(acc_gate) * acc_up, with a second weight (act: SiLU or GELU)
+    kStoreAct = 3,     // out = act(acc): a feed-forward without a gate
 };
 
 constexpr int TM = 64, TN = 64, TK = 16, PAD = 4;
@@ -20,7 +21,13 @@ constexpr int TM = 64, TN = 64, TK = 16, PAD = 4;
 template <typename TA, typename TW, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, const TW* __restrict__ W2,
-               TO* __restrict__ out, int ldo, int M, int N, int K, const Ending e) {
+               TO* __restrict__ out, int ldo, int M, int N, int K, const Ending e,
+               long batch_a, long batch_w, long batch_o) {
+    // blockIdx.z: one of several products of the same sizes (a head each), operands `batch_*` elements apart
+    A += (size_t)blockIdx.z * batch_a;
+    W += (size_t)blockIdx.z * batch_w;
+    if (MODE == kSwiGLU) W2 += (size_t)blockIdx.z * batch_w;
+    out += (size_t)blockIdx.z * batch_o;
     __shared__ float As[TK][TM + PAD];
     __shared__ float Ws[TK][TN + PAD];
     __shared__ float Ws2[MODE == kSwiGLU ? TK : 1][TN + PAD];
@@ -79,6 +86,8 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
                 *o = from_float<TO>(r);
             } else if (MODE == kAccumulate) {
                 *o = from_float<TO>(to_float(*o) + r);
+            } else if (MODE == kStoreAct) {
+                *o = from_float<TO>(gate_activation(r, e.act));
             } else {
                 *o = from_float<TO>(gate_activation(r, e.act) * (acc2[i][j] + ending_bias(e.bias2, e.bias_dtype, n)));
             }
@@ -88,14 +97,17 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
 
 template <typename TA, typename TW, typename TO>
 static int launch_gemm(int mode, const void* A, int lda, const void* W, const void* W2, void* out, int ldo,
-                       int M, int N, int K, const Ending& e, cudaStream_t stream) {
-    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
+                       int M, int N, int K, const Ending& e, cudaStream_t stream,
+                       int batch = 1, long batch_a = 0, long batch_w = 0, long batch_o = 0) {
+    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
     if (mode == kStore)
-        gemm_nt_kernel<TA, TW, TO, kStore><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e);
+        gemm_nt_kernel<TA, TW, TO, kStore><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e, batch_a, batch_w, batch_o);
     else if (mode == kAccumulate)
-        gemm_nt_kernel<TA, TW, TO, kAccumulate><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e);
+        gemm_nt_kernel<TA, TW, TO, kAccumulate><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e, batch_a, batch_w, batch_o);
     else if (mode == kSwiGLU)
-        gemm_nt_kernel<TA, TW, TO, kSwiGLU><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, (const TW*)W2, (TO*)out, ldo, M, N, K, e);
+        gemm_nt_kernel<TA, TW, TO, kSwiGLU><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, (const TW*)W2, (TO*)out, ldo, M, N, K, e, batch_a, batch_w, batch_o);
+    else if (mode == kStoreAct)
+        gemm_nt_kernel<TA, TW, TO, kStoreAct><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e, batch_a, batch_w, batch_o);
     else
         return fail("gemm_simt: unknown mode %d", mode);
     MDMA_LAUNCH_OK("gemm_simt");
@@ -124,4 +136,23 @@ extern "C" int mdma_gemm_simt(int mode, const void* A, int a_dtype, int lda, con
     if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kF32)
         return launch_gemm<__nv_bfloat16, __nv_bfloat16, float>(mode, A, lda, W, W2, out, ldo, M, N, K, e, stream);
     return fail("gemm_simt: unsupported dtypes a=%d w=%d out=%d", a_dtype, w_dtype, out_dtype);
+}
+
+// `batch` products of the same sizes in one launch: product z reads A + z * batch_a (rows `lda` apart),
+// W + z * batch_w ([N, K], contiguous) and writes out + z * batch_o (rows `ldo` apart).  A projection
+// applied head by head is one call: the heads lie side by side in the rows of A and of out.
+extern "C" int mdma_gemm_simt_batched(const void* A, int a_dtype, int lda, long batch_a, const void* W, int w_dtype,
+                                      long batch_w, void* out, int out_dtype, int ldo, long batch_o, int batch,
+                                      int M, int N, int K, cudaStream_t stream) {
+    MDMA_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm_simt_batched: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    MDMA_REQUIRE((size_t)((M + TM - 1) / TM) <= 65535, "gemm_simt_batched: too many rows (%d)", M);
+    if (M == 0) return 0;
+    const Ending e{nullptr, nullptr, kF32, kActSilu};
+    if (a_dtype == kF32 && w_dtype == kF32 && out_dtype == kF32)
+        return launch_gemm<float, float, float>(kStore, A, lda, W, nullptr, out, ldo, M, N, K, e, stream, batch, batch_a, batch_w, batch_o);
+    if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kBF16)
+        return launch_gemm<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(kStore, A, lda, W, nullptr, out, ldo, M, N, K, e, stream, batch, batch_a, batch_w, batch_o);
+    if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kF32)
+        return launch_gemm<__nv_bfloat16, __nv_bfloat16, float>(kStore, A, lda, W, nullptr, out, ldo, M, N, K, e, stream, batch, batch_a, batch_w, batch_o);
+    return fail("gemm_simt_batched: unsupported dtypes a=%d w=%d out=%d", a_dtype, w_dtype, out_dtype);
 }

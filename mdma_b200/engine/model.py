@@ -10,7 +10,7 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
 from ..cache import KVNeed, SequenceCache, StateNeed
 from ..parts.base import Part, Runtime
-from ..registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
+from ..registry import BLOCKS, EMBEDDINGS, HEADS, JUNCTIONS, NORMS
 from ..spec import ModelSpec, TensorSpec
 
 
@@ -27,7 +27,14 @@ class DecoderModel:
         self.blocks = [BLOCKS.get(layer.block)(layer) for layer in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm)
         self.head = HEADS.get(spec.lm_head.kind)(spec.lm_head)
+        self.junctions = [JUNCTIONS.get(j.kind)(j) for j in spec.junctions]
+        # junctions that read the embedding's output: it is then kept beside the residual stream
+        self.keeps_embedding = any(getattr(j, "needs_embedding", False) for j in self.junctions)
+        # called as on_layer(n, x) after the n-th run of the schedule with the residual rows (a debugging aid)
+        self.on_layer = None
         for n, entry in enumerate(spec.schedule):
+            if entry.junction is not None and not 0 <= entry.junction < len(self.junctions):
+                raise ValueError(f"schedule entry {n} names junction {entry.junction}, there are {len(self.junctions)}")
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {n} names layer {entry.layer}, there are {len(self.blocks)}")
             if entry.cache is not None:
@@ -36,7 +43,7 @@ class DecoderModel:
 
     # ---- inventory -----------------------------------------------------
     def all_parts(self) -> list[Part]:
-        tops = [self.embedding, self.final_norm, self.head]
+        tops = [self.embedding, self.final_norm, self.head] + list(self.junctions)
         for b in self.blocks:
             tops.extend(b.parts())
         return [p for top in tops for p in _walk(top)]
@@ -60,13 +67,21 @@ class DecoderModel:
         return needs
 
     def state_needs(self) -> list[Optional[StateNeed]]:
-        return [self.blocks[e.layer].mixer.state_need() for e in self.spec.schedule]
+        """Per schedule entry: the fixed-size state of its run.  An arrangement that keeps state of
+        its own beside the mixer's (a token shift's last row) answers for both."""
+        needs = []
+        for e in self.spec.schedule:
+            block = self.blocks[e.layer]
+            needs.append(block.state_need() if hasattr(block, "state_need") else block.mixer.state_need())
+        return needs
 
     def workspace_columns(self) -> dict[str, tuple[int, str]]:
         # the model's own: the residual stream and the normed rows the head reads; the rest is asked for by
         # the block arrangements and the parts
         cols: dict[str, tuple[int, str]] = {"x": (self.spec.hidden_size, "f32"),
                                              "h_rows": (self.spec.hidden_size, "act")}
+        if self.keeps_embedding:
+            cols["x_embedded"] = (self.spec.hidden_size, "f32")
         askers = [b for b in self.blocks if hasattr(b, "workspace")] + self.all_parts()
         for part in askers:
             for name, (c, kind) in part.workspace().items():
@@ -144,15 +159,29 @@ class DecoderModel:
         and into it; write logits of ctx.want_rows into `logits` [n_want, vocab]."""
         x = ctx.buf("x", self.spec.hidden_size, torch.float32)
         self.embedding.forward(ctx, ctx.ids, x)
+        x0 = None
+        if self.keeps_embedding:
+            x0 = ctx.buf("x_embedded", self.spec.hidden_size, torch.float32)
+            self.embedding.forward(ctx, ctx.ids, x0)
         for n, entry in enumerate(self.spec.schedule):
             site = n if entry.cache is None else entry.cache
             block = self.blocks[entry.layer]
+            if entry.junction is not None:
+                if ctx.rt.gemm == "tensor":
+                    from .. import ops_tensor
+                    ops_tensor.flush_pending(x.device, ctx.rt.tc)
+                self.junctions[entry.junction].forward(ctx, x, x0, entry.junction_arg)
             if ctx.rt.gemm == "tensor" and not getattr(block, "handles_pending", False):
                 # a product of the block before may have left partial sums of x for a norm to add up; an
                 # arrangement that does not know of that gets x complete
                 from .. import ops_tensor
                 ops_tensor.flush_pending(x.device, ctx.rt.tc)
             block.forward(ctx, x, cache.view(site, state_site=n), owns_cache=entry.cache is None)
+            if self.on_layer is not None:
+                if ctx.rt.gemm == "tensor":
+                    from .. import ops_tensor
+                    ops_tensor.flush_pending(x.device, ctx.rt.tc)
+                self.on_layer(n, x[:ctx.n_tokens])
         if ctx.rt.gemm == "tensor":
             from .. import ops_tensor
             ops_tensor.flush_pending(x.device, ctx.rt.tc)

@@ -250,3 +250,184 @@ def advance_decode(tokens: torch.Tensor, ids: torch.Tensor, tok_pos: torch.Tenso
     assert ring is None or (ring.dtype == torch.int32 and ring.is_contiguous() and counter.dtype == torch.int32)
     _call("core", "mdma_advance_decode", _ptr(tokens), _ptr(ids), _ptr(tok_pos), _ptr(seq_pos0), _i(n),
           _i(words), _ptr(ring), _i(rows), _ptr(counter), _stream())
+
+
+# ---- layers with per-sequence state, and the small steps around them (csrc/sequence_mix.cu) ---------------
+GEMM_STORE_ACT = 3        # out = act(a W^T + b): CUDA-core product only
+
+
+def _state(state: torch.Tensor):
+    """Pointer and row stride of a per-sequence state [slots, n] (a view of wider rows is fine)."""
+    assert state.is_cuda and state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    return _ptr(state), ctypes.c_long(state.stride(0))
+
+
+def _same_dtype(*vectors):
+    dt = vectors[0].dtype
+    for v in vectors:
+        assert v.is_cuda and v.is_contiguous() and v.dtype == dt, "the small vectors of a part are kept in one dtype"
+    return dtype_code(dt)
+
+
+def dyt_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+    """out[i] = tanh(alpha * x[rows[i]] or x[i]) * w + b; x is the float residual stream."""
+    _need_cuda(x, w, b, alpha, out, rows)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    width = x.shape[-1]
+    assert w.numel() == width and b.numel() == width and alpha.numel() == 1 and out.shape[-1] == width
+    n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert out.shape[0] >= n and (rows is None or rows.dtype == torch.int32)
+    _call("core", "mdma_dyt_norm", _ptr(x), _ptr(w), _ptr(b), _ptr(alpha), _i(_same_dtype(w, b, alpha)), _ptr(rows),
+          _ptr(out), _i(dtype_code(out.dtype)), _i(n), _i(width), _stream())
+
+
+def dyt_shift(x, w, b, alpha, mu, tok_seq, seq_start, seq_slot, state, h, hs, n_rows: int) -> None:
+    """h = dyt(x) and hs = h + (h' - h) * mu in one pass (h': the row before, or the kept row of `state`)."""
+    _need_cuda(x, w, b, alpha, mu, tok_seq, seq_start, seq_slot, state, h, hs)
+    width = x.shape[-1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and h.is_contiguous() and hs.is_contiguous()
+    assert h.dtype == hs.dtype and h.shape[1] == hs.shape[1] == width and mu.numel() == width
+    sp, ss = _state(state)
+    _call("core", "mdma_dyt_shift", _ptr(x), _ptr(w), _ptr(b), _ptr(alpha), _ptr(mu), _i(_same_dtype(w, b, alpha, mu)),
+          _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(h), _ptr(hs), _i(dtype_code(h.dtype)),
+          _i(n_rows), _i(width), _stream())
+
+
+def token_shift(h, mu, tok_seq, seq_start, seq_slot, state, hs, n_rows: int) -> None:
+    """hs[t] = h[t] + (h' - h[t]) * mu, h' = h[t-1] within the step, else the sequence's kept row."""
+    _need_cuda(h, mu, tok_seq, seq_start, seq_slot, state, hs)
+    width = h.shape[1]
+    assert h.is_contiguous() and hs.is_contiguous() and hs.dtype == h.dtype and hs.shape[1] == width and mu.numel() == width
+    sp, ss = _state(state)
+    _call("core", "mdma_token_shift", _ptr(h), _i(dtype_code(h.dtype)), _ptr(mu), _i(dtype_code(mu.dtype)),
+          _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(hs), _i(n_rows), _i(width), _stream())
+
+
+def keep_last_rows(rows, seq_start, seq_slot, state, n_seqs: int) -> None:
+    """state[slot] = the last row each sequence brought."""
+    _need_cuda(rows, seq_start, seq_slot, state)
+    assert rows.is_contiguous()
+    sp, ss = _state(state)
+    _call("core", "mdma_keep_last_rows", _ptr(rows), _i(dtype_code(rows.dtype)), _ptr(seq_start), _ptr(seq_slot),
+          sp, ss, _i(n_seqs), _i(rows.shape[1]), _stream())
+
+
+def gated_add(x, g, y, n_rows: int, keep_rows=None, tok_seq=None, seq_start=None, seq_slot=None, state=None) -> None:
+    """x += sigmoid(g) * y (x, y float).  With `keep_rows` each sequence's last row of it goes to `state`."""
+    _need_cuda(x, g, y, keep_rows, tok_seq, seq_start, seq_slot, state)
+    width = x.shape[1]
+    assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and g.is_contiguous()
+    assert g.shape[1] == width and y.shape[1] == width
+    sp, ss = (_ptr(None), ctypes.c_long(0))
+    if keep_rows is not None:
+        assert keep_rows.is_contiguous() and keep_rows.shape[1] == width
+        sp, ss = _state(state)
+    _call("core", "mdma_gated_add", _ptr(x), _ptr(g), _i(dtype_code(g.dtype)), _ptr(y), _i(n_rows), _i(width),
+          _ptr(keep_rows), _i(dtype_code(keep_rows.dtype) if keep_rows is not None else F32), _ptr(tok_seq),
+          _ptr(seq_start), _ptr(seq_slot), sp, ss, _stream())
+
+
+def activation(v: torch.Tensor, n_rows: int, act: int) -> None:
+    """v[:n_rows] = act(v[:n_rows]) in place."""
+    _need_cuda(v)
+    assert v.is_contiguous()
+    _call("core", "mdma_activation", _ptr(v), _i(dtype_code(v.dtype)), ctypes.c_long(n_rows * v.shape[1]), _i(act), _stream())
+
+
+def softcap(logits: torch.Tensor, n_rows: int, cap: float) -> None:
+    """logits[:n_rows] = cap * tanh(logits / cap) in place (float)."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _call("core", "mdma_softcap", _ptr(logits), ctypes.c_long(n_rows * logits.shape[1]), _f(cap), _stream())
+
+
+def pack_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    """out[t] = [a[t] | b[t]] in out's dtype; a and b are float rows of one width."""
+    _need_cuda(a, b, out)
+    width = a.shape[1]
+    assert a.dtype == b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
+    assert b.shape[1] == width and out.shape[1] == 2 * width
+    _call("core", "mdma_pack_pair", _ptr(a), _ptr(b), _ptr(out), _i(dtype_code(out.dtype)), _i(n_rows), _i(width), _stream())
+
+
+def mingru_scan(p, bz, bu, seq_start, seq_slot, state, out, n_seqs: int, width: int) -> None:
+    """p [T, 3*width] float = the three projections (z | u | g); runs S = (1-z) S + z cand over each
+    sequence's rows and writes S * silu(g)."""
+    _need_cuda(p, bz, bu, seq_start, seq_slot, state, out)
+    assert p.dtype == torch.float32 and p.stride(1) == 1 and p.shape[1] == 3 * width and out.is_contiguous() and out.shape[1] == width
+    sp, ss = _state(state)
+    _call("core", "mdma_mingru_scan", _ptr(p), _i(p.stride(0)), _ptr(bz), _ptr(bu), _i(_same_dtype(bz, bu)),
+          _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out), _i(dtype_code(out.dtype)), _i(n_seqs), _i(width), _stream())
+
+
+def causal_conv_silu(proj, in_col: int, w, b, taps: int, channels: int, tok_seq, seq_start, seq_slot, state, out,
+                     n_rows: int, n_seqs: int) -> None:
+    """out[t, c] = silu(bias + sum_j w[c, j] * input(t - taps + 1 + j, c)) over columns in_col.. of the float
+    projection rows; inputs before the step come from `state` ([taps-1, channels] per slot), which is then
+    brought up to date."""
+    _need_cuda(proj, w, b, tok_seq, seq_start, seq_slot, state, out)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
+    assert w.is_contiguous() and tuple(w.shape) == (channels, taps) and b.numel() == channels and out.shape[1] == channels
+    sp, ss = _state(state)
+    _call("core", "mdma_causal_conv_silu", _ptr(proj), _i(proj.stride(0)), _i(in_col), _ptr(w), _i(dtype_code(w.dtype)),
+          _ptr(b), _i(dtype_code(b.dtype)), _i(taps), _i(channels), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot),
+          sp, ss, _ptr(out), _i(n_rows), _i(n_seqs), _stream(), launches=2 if taps > 1 else 1)
+
+
+def mamba2_scan(conv, proj, dt_col: int, dt_bias, a_log, d, seq_start, seq_slot, state, y, n_seqs: int, heads: int,
+                vdim: int, n_state: int, groups: int) -> None:
+    """The selective scan over each sequence's rows; `conv` rows are [x | B | C] after the convolution,
+    `proj` holds the raw step sizes at columns dt_col + head; state [slots, heads * n_state * vdim] float."""
+    _need_cuda(conv, proj, dt_bias, a_log, d, seq_start, seq_slot, state, y)
+    assert conv.dtype == proj.dtype == y.dtype == torch.float32 and conv.stride(1) == 1 and proj.stride(1) == 1
+    assert y.is_contiguous() and y.shape[1] == heads * vdim and conv.shape[1] == heads * vdim + 2 * groups * n_state
+    sp, ss = _state(state)
+    _call("core", "mdma_mamba2_scan", _ptr(conv), _i(conv.stride(0)), _ptr(proj), _i(proj.stride(0)), _i(dt_col),
+          _ptr(dt_bias), _ptr(a_log), _ptr(d), _i(_same_dtype(dt_bias, a_log, d)), _ptr(seq_start), _ptr(seq_slot),
+          sp, ss, _ptr(y), _i(n_seqs), _i(heads), _i(vdim), _i(n_state), _i(groups), _stream())
+
+
+def gated_group_rmsnorm(y, z, w, out, n_rows: int, groups: int, eps: float) -> None:
+    """out = rms_unit_per_part(y * silu(z)) * w; y and z float rows (z may be a view of wider rows)."""
+    _need_cuda(y, z, w, out)
+    width = y.shape[1]
+    assert y.dtype == z.dtype == torch.float32 and y.stride(1) == 1 and z.stride(1) == 1 and z.shape[1] == width
+    assert out.is_contiguous() and out.shape[1] == width and w.numel() == width and w.is_contiguous()
+    _call("core", "mdma_gated_group_rmsnorm", _ptr(y), _i(y.stride(0)), _ptr(z), _i(z.stride(0)), _ptr(w),
+          _i(dtype_code(w.dtype)), _ptr(out), _i(dtype_code(out.dtype)), _i(n_rows), _i(width), _i(groups), _f(eps), _stream())
+
+
+def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int) -> None:
+    """out[:m, z*N:(z+1)*N] = a[:m, z*K:(z+1)*K] @ w[z].T for every z: w [batch, N, K]; the pieces of a
+    row (one per head) lie side by side in a and in out."""
+    _need_cuda(a, w, out)
+    batch, N, K = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
+    assert a.shape[1] >= batch * K and out.shape[1] >= batch * N and a.shape[0] >= m and out.shape[0] >= m
+    _call("core", "mdma_gemm_simt_batched", _ptr(a), _i(dtype_code(a.dtype)), _i(a.stride(0)), ctypes.c_long(K),
+          _ptr(w), _i(dtype_code(w.dtype)), ctypes.c_long(N * K), _ptr(out), _i(dtype_code(out.dtype)),
+          _i(out.stride(0)), ctypes.c_long(N), _i(batch), _i(m), _i(N), _i(K), _stream())
+
+
+# ---- attention over a cached latent (csrc/latent_attention.cu) ------------------------------------------------
+def latent_norm_store(proj, col0: int, w, eps: float, rank: int, tok_seq, tok_pos, seq_slot, page_table,
+                      max_pages: int, page_size: int, cache, n_tokens: int) -> None:
+    """cache[row of token] = rms_unit(proj[t, col0:col0+rank]) * w."""
+    _need_cuda(proj, w, tok_seq, tok_pos, seq_slot, page_table, cache)
+    assert proj.stride(1) == 1 and cache.is_contiguous() and cache.dtype == proj.dtype and w.numel() == rank
+    _call("core", "mdma_latent_norm_store", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(col0),
+          _ptr(w), _i(dtype_code(w.dtype)), _f(eps), _i(rank), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot),
+          _ptr(page_table), _i(max_pages), _i(page_size), _ptr(cache), _i(n_tokens), _stream())
+
+
+def latent_attention(q, cache, sink, tok_seq, tok_pos, seq_slot, page_table, max_pages: int, page_size: int, out,
+                     n_tokens: int, n_heads: int, rank: int, window: int, scale: float) -> None:
+    """q [T, heads*rank]: queries already mapped into the latent; out [T, heads*rank]: the weighted sums of
+    cached latents, softmax with one sink term per head in the denominator."""
+    _need_cuda(q, cache, sink, tok_seq, tok_pos, seq_slot, page_table, out)
+    assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == cache.dtype and cache.is_contiguous()
+    assert out.shape[1] == n_heads * rank and sink.numel() == n_heads and sink.is_contiguous()
+    _call("core", "mdma_latent_attention", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(cache), _ptr(sink),
+          _i(dtype_code(sink.dtype)), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
+          _i(page_size), _ptr(out), _i(n_tokens), _i(n_heads), _i(rank), _i(window), _f(scale), _stream())

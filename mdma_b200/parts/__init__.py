@@ -1,5 +1,5 @@
 """Parts a layer is put together from; importing this package registers them."""
-from . import attention, block, embedding, mlp, norm, rotary  # noqa: F401
+from . import attention, block, embedding, gating, latent_attention, mlp, norm, recurrent, rotary  # noqa: F401
 from .base import Part, Runtime
 from .linear import Linear
 

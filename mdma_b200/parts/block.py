@@ -1,9 +1,12 @@
 """How a layer's parts are arranged.  "prenorm": x += mixer(norm(x)); x +=
 feed_forward(norm(x)), the residual stream x kept in float
-(src/model/arch/llama.rs:181-231)."""
+(src/model/arch/llama.rs:181-231).  "shift_gated": the same with a token shift
+in front of the mixer and a learned gate on each sublayer's result."""
 from __future__ import annotations
 
-from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+import torch
+
+from ..registry import AUXILIARIES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from ..spec import LayerSpec
 
 
@@ -41,3 +44,86 @@ class PreNormBlock:
         if ctx.rt.gemm == "tensor" and not getattr(norm, "fuses_pending", False):
             from .. import ops_tensor
             ops_tensor.flush_pending(x.device, ctx.rt.tc)
+
+
+@BLOCKS.register("shift_gated")
+class ShiftGatedBlock:
+    """Pre-norm with a token shift and gated residuals:
+
+        h = norm1(x);  x += sigmoid(Wg1 h + b1) * mixer(shift(h))
+        h = norm2(x);  x += sigmoid(Wg2 h + b2) * feed_forward(h)       (if the layer has one)
+
+    The gates read h as the norm hands it out, before the shift; only the mixer reads shifted rows.
+    Parts beyond a layer's four come from `LayerSpec.extras`: "shift" (token_shift), "mixer_gate" and
+    "ffn_gate" (residual_gate).  The run's state rows hold the shift's last h first, then the mixer's
+    own state.  Mixers and feed-forwards that offer `produce` (store their result as float rows) are
+    used that way; others run into a zeroed buffer through their ordinary `forward`."""
+
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer)
+        self.width = int(spec.mixer_norm.params["width"])
+        self.shift = AUXILIARIES.get(spec.extras["shift"].kind)(spec.extras["shift"])
+        self.mixer_gate = AUXILIARIES.get(spec.extras["mixer_gate"].kind)(spec.extras["mixer_gate"])
+        self.ffn_norm = self.ffn = self.ffn_gate = None
+        if spec.ffn is not None:
+            self.ffn_norm = NORMS.get(spec.ffn_norm.kind)(spec.ffn_norm)
+            self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn)
+            self.ffn_gate = AUXILIARIES.get(spec.extras["ffn_gate"].kind)(spec.extras["ffn_gate"])
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.shift, self.mixer_gate, self.ffn_norm, self.ffn,
+                            self.ffn_gate) if p is not None]
+
+    def workspace(self):
+        W = self.width
+        return {"normed": (W, "act"), "shifted": (W, "act"), "gate": (W, "act"), "sublayer": (W, "f32")}
+
+    def state_need(self):
+        from ..cache import StateNeed
+        inner = self.mixer.state_need()
+        own = self.shift.state_floats()
+        if inner is None:
+            return StateNeed((own,), torch.float32)
+        if inner.dtype != torch.float32:
+            raise ValueError("the arrangement keeps its state in float rows; so must its mixer")
+        n = 1
+        for d in inner.shape:
+            n *= int(d)
+        return StateNeed((own + n,), torch.float32)
+
+    def forward(self, ctx, x, view, owns_cache=True):
+        import dataclasses
+        n, W = ctx.n_tokens, self.width
+        own = self.shift.state_floats()
+        shift_state = view.state[:, :own]
+        mixer_view = dataclasses.replace(view, state=view.state[:, own:] if view.state.shape[1] > own else None)
+        h, hs, g = ctx.buf("normed", W), ctx.buf("shifted", W), ctx.buf("gate", W)
+        y = ctx.buf("sublayer", W, torch.float32)
+        if hasattr(self.mixer_norm, "forward_shifted"):
+            self.mixer_norm.forward_shifted(ctx, x, h, hs, self.shift.mu, shift_state)
+        else:
+            self.mixer_norm.forward(ctx, x, h)
+            self.shift.forward(ctx, h, hs, shift_state)
+        self.mixer_gate.project(ctx, h, g)
+        self._run(ctx, self.mixer, hs, y, mixer_view, owns_cache)
+        # the shift's kept row is replaced only now, after the launch that read it
+        self.mixer_gate.apply(ctx, x, g, y, keep_rows=h, state=shift_state)
+        if self.ffn is None:
+            return
+        self.ffn_norm.forward(ctx, x, h)
+        self.ffn_gate.project(ctx, h, g)
+        self._run(ctx, self.ffn, h, y)
+        self.ffn_gate.apply(ctx, x, g, y)
+
+    @staticmethod
+    def _run(ctx, part, h, y, *more):
+        if hasattr(part, "produce"):
+            part.produce(ctx, h, y, *more)
+            return
+        y[:ctx.n_tokens].zero_()
+        part.forward(ctx, h, y, *more)
+        if ctx.rt.gemm == "tensor":
+            from .. import ops_tensor
+            ops_tensor.flush_pending(y.device, ctx.rt.tc)

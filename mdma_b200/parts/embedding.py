@@ -35,6 +35,10 @@ class LMHead(Part):
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab, self.width = int(self.params["vocab_size"]), int(self.params["width"])
+        # `softcap` c: logits <- c * tanh(logits / c); None or 0: none
+        self.softcap = float(self.params.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError("the logits' soft cap must be positive")
 
     def tensor_specs(self):
         return {"weight": TensorSpec((self.vocab, self.width))}
@@ -45,6 +49,10 @@ class LMHead(Part):
 
     def forward(self, ctx, h_rows, logits, n_rows):
         self.proj.store(h_rows, logits, n_rows)
+        if self.softcap:
+            if not logits.is_contiguous():
+                raise ops.KernelError("the soft cap takes contiguous logit rows")
+            ops.softcap(logits, n_rows, self.softcap)
 
     def resident_tensors(self):
         return [self.proj.w]

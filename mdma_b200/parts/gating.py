@@ -1,0 +1,109 @@
+"""Small parts around a sublayer: the token shift in front of a mixer, the gate
+on a sublayer's result, and the junction that re-enters a looped stack.
+
+Token shift: what the mixer reads is h_t + (h_(t-1) - h_t) * mu, mu a learned
+vector, h the normed rows as the arrangement hands them out, h_(-1) = 0.  The
+last h of a sequence is part of its state (`width` floats).
+
+Residual gate: the sublayer's result is multiplied by sigmoid(W h + b) before
+it is added to the residual stream.
+
+Loop input: before a pass over a looped stack of layers, x <- W [x ; x0] + s_t,
+x0 the embedding's output and s_t a learned vector per pass.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..registry import AUXILIARIES, JUNCTIONS
+from ..spec import TensorSpec
+from .base import Part
+from .linear import Linear
+
+
+@AUXILIARIES.register("token_shift")
+class TokenShift(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(self.params["width"])
+
+    def tensor_specs(self):
+        return {"mu": TensorSpec((self.width,), "vector", "normal")}
+
+    def state_floats(self) -> int:
+        return self.width
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.mu = tensors["mu"]
+
+    def forward(self, ctx, h, hs, state):
+        """hs = shifted h; `state` [slots, width] holds each sequence's last h of the step before."""
+        ops.token_shift(h, self.mu, ctx.tok_seq, ctx.seq_start, ctx.seq_slot, state, hs, ctx.n_tokens)
+
+    def keep(self, ctx, h, state):
+        """After everything that reads the old state has run: each sequence's last h goes to the state."""
+        ops.keep_last_rows(h, ctx.seq_start, ctx.seq_slot, state, ctx.n_seqs)
+
+    def resident_tensors(self):
+        return [self.mu]
+
+
+@AUXILIARIES.register("residual_gate")
+class ResidualGate(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(self.params["width"])
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.width, self.width)), "bias": TensorSpec((self.width,), "vector", "normal")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.proj = Linear(tensors["weight"], rt, bias=tensors["bias"])
+
+    def project(self, ctx, h, g):
+        """g = W h + b (the sigmoid is taken where the gate is applied)."""
+        self.proj.store(h, g, ctx.n_tokens)
+
+    def apply(self, ctx, x, g, y, keep_rows=None, state=None):
+        """x += sigmoid(g) * y; with `keep_rows`, each sequence's last row of it goes to `state` in the same pass."""
+        if keep_rows is None:
+            ops.gated_add(x, g, y, ctx.n_tokens)
+        else:
+            ops.gated_add(x, g, y, ctx.n_tokens, keep_rows, ctx.tok_seq, ctx.seq_start, ctx.seq_slot, state)
+
+    def resident_tensors(self):
+        return [self.proj.w, self.proj.bias]
+
+
+@JUNCTIONS.register("loop_input")
+class LoopInput(Part):
+    """x <- W [x ; x0] + step[t] before pass t of a looped stack.  W is [width, 2 width] with x's
+    columns first; `step` is [passes, width]."""
+    needs_embedding = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width, self.passes = int(self.params["width"]), int(self.params["passes"])
+
+    def tensor_specs(self):
+        return {"in": TensorSpec((self.width, 2 * self.width)),
+                "step": TensorSpec((self.passes, self.width), "vector", "normal")}
+
+    def workspace(self):
+        return {"loop_pair": (2 * self.width, "act")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.step = tensors["step"]
+        self.proj = [Linear(tensors["in"], rt, bias=self.step[t]) for t in range(self.passes)]
+
+    def forward(self, ctx, x, x0, t: int):
+        pair = ctx.buf("loop_pair", 2 * self.width)
+        ops.pack_pair(x, x0, pair, ctx.n_tokens)
+        self.proj[t].store(pair, x, ctx.n_tokens)
+
+    def resident_tensors(self):
+        return [self.proj[0].w, self.step] if self.proj else [self.step]

@@ -47,6 +47,14 @@ class Linear:
         """x += a W^T.  Deferred by default: the norm that reads x next adds the partial sums."""
         self._run(ops.GEMM_ACCUMULATE, a, x, m, defer)
 
+    def store_act(self, a, out, m):
+        """out = act(a W^T + b): a feed-forward's first product when it has no gate."""
+        if self._tensor_ok:
+            self._run(ops.GEMM_STORE, a, out, m)
+            ops.activation(out, m, self.act)
+        else:
+            self._run(ops.GEMM_STORE_ACT, a, out, m)
+
     def gated(self, a, out, m):
         """out = act(a W^T) * (a W2^T)."""
         self._run(ops.GEMM_SWIGLU, a, out, m)

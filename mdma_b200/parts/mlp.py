@@ -1,9 +1,13 @@
-"""Gated feed-forward: act = f(h Wg^T) * (h Wu^T); x += act Wd^T, f = SiLU
+"""Feed-forwards.
+
+Gated: act = f(h Wg^T) * (h Wu^T); x += act Wd^T, f = SiLU
 (src/model/arch/llama.rs:222-230, src/backend/cpu.rs:447-458).  Dense: every
 token uses the same three matrices.  The two first products and the
 activation run as one kernel.  Parameters beyond the reference's Llama:
 `activation` ("silu", "gelu_tanh") and `bias` (a vector added after each of
-the three products)."""
+the three products).
+
+Dense (`dense_mlp`): x += act(h Wu^T) Wd^T, no gate; `activation` as above."""
 from __future__ import annotations
 
 from .. import ops
@@ -52,3 +56,43 @@ class GatedMLP(Part):
     def resident_tensors(self):
         return [t for t in (self.gate_up.w, self.gate_up.w2, self.down.w, self.gate_up.bias, self.gate_up.bias2,
                             self.down.bias) if t is not None]
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(Part):
+    """act(h Wu^T) Wd^T.  `produce` stores the result as float rows (for an arrangement that scales
+    it before the residual add); `forward` adds it into the residual stream."""
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.params["hidden_size"])
+        self.inner = int(self.params["intermediate_size"])
+        self.activation = str(self.params.get("activation", "gelu_tanh"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not implemented (have {sorted(ops.ACTIVATIONS)})")
+
+    def tensor_specs(self):
+        return {"up": TensorSpec((self.inner, self.hidden)), "down": TensorSpec((self.hidden, self.inner))}
+
+    def workspace(self):
+        # a buffer per size: rows of a shared, wider buffer would not be contiguous
+        return {f"dense_act_{self.inner}": (self.inner, "act")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.up = Linear(tensors["up"], rt, activation=self.activation)
+        self.down = Linear(tensors["down"], rt)
+
+    def produce(self, ctx, h, out):
+        act = ctx.buf(f"dense_act_{self.inner}", self.inner)
+        self.up.store_act(h, act, ctx.n_tokens)
+        self.down.store(act, out, ctx.n_tokens)
+
+    def forward(self, ctx, h, x):
+        act = ctx.buf(f"dense_act_{self.inner}", self.inner)
+        self.up.store_act(h, act, ctx.n_tokens)
+        self.down.accumulate(act, x, ctx.n_tokens)
+
+    def resident_tensors(self):
+        return [self.up.w, self.down.w]

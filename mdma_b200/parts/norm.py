@@ -1,6 +1,10 @@
-"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w (src/backend/cpu.rs:388-401;
-no +1 on the weight, no mean subtraction).  Reads the float residual stream,
-writes the compute dtype; sums in float."""
+"""Norms.  Both read the float residual stream and write the compute dtype.
+
+RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w (src/backend/cpu.rs:388-401;
+no +1 on the weight, no mean subtraction); sums in float.
+
+Dynamic tanh: y = tanh(alpha * x) * w + b with a learned scalar alpha; no mean,
+no variance, nothing summed over the row."""
 from __future__ import annotations
 
 from .. import ops
@@ -39,3 +43,34 @@ class RMSNorm(Part):
 
     def resident_tensors(self):
         return [self.weight]
+
+
+@NORMS.register("dyt")
+class DynamicTanh(Part):
+    """tanh(alpha * x) * w + b.  Because nothing is summed over a row, the arrangement that shifts
+    tokens may ask for the shifted rows in the same pass (`forward_shifted`)."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(self.params["width"])
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.width,), "vector"),
+                "b": TensorSpec((self.width,), "vector", "zeros"),
+                "alpha": TensorSpec((), "vector", "ones")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight, self.b, self.alpha = tensors["weight"], tensors["b"], tensors["alpha"]
+
+    def forward(self, ctx, x, out, rows=None, n_rows=None):
+        n = n_rows if n_rows is not None else (None if rows is not None else ctx.n_tokens)
+        ops.dyt_norm(x, self.weight, self.b, self.alpha, out, rows, n)
+
+    def forward_shifted(self, ctx, x, h, hs, mu, state):
+        """h = norm(x) and hs = h + (h' - h) * mu, h' the normed row before (or the kept one)."""
+        ops.dyt_shift(x, self.weight, self.b, self.alpha, mu, ctx.tok_seq, ctx.seq_start, ctx.seq_slot, state,
+                      h, hs, ctx.n_tokens)
+
+    def resident_tensors(self):
+        return [self.weight, self.b, self.alpha]

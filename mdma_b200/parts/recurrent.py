@@ -1,0 +1,166 @@
+"""Mixers that carry fixed-size state from token to token instead of keys and values.
+
+minGRU (`mingru`): a gated recurrence whose gates read the current token only,
+    z = sigmoid(Wz h + bz),  u = Wx h + bx,  c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0),
+    S_t = (1 - z) S_(t-1) + z c,   out = Wo (S_t * silu(Wg h));  S has `width` numbers.
+
+Mamba-2 (`mamba2`), the state-space-duality form: Win h = [z | x | B | C | dt] with
+inner = heads * vdim, groups G and state size N; x, B, C go through a short causal
+convolution per channel and silu; per head h (group h // (heads / G)),
+    dt = softplus(dt + dt_bias),  S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T,
+    y_t = S_t^T C_t + D x_t;
+y * silu(z) is divided by its root mean square in `norm_groups` equal parts, weighted and
+sent through Wo.  State: S [heads, N, vdim] and the convolution's last taps-1 inputs.
+
+The state is float, zero at a sequence's start, kept per slot by the cache; everything
+that enters the recurrences is float in both engines (the projections write float rows).
+Both offer `produce` (the result as float rows) beside the ordinary `forward`.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import StateNeed
+from ..registry import MIXERS
+from ..spec import TensorSpec
+from .base import Part
+from .linear import Linear
+
+
+class _StatefulMixer(Part):
+    graph_safe = True      # forward reads no host-side per-step values
+
+    def kv_need(self):
+        return None
+
+    def forward(self, ctx, h, x, view, owns_cache=True):
+        self._run(ctx, h, x, view, accumulate=True)
+
+    def produce(self, ctx, h, out, view, owns_cache=True):
+        self._run(ctx, h, out, view, accumulate=False)
+
+    def _finish(self, proj, a, target, n, accumulate):
+        if accumulate:
+            proj.accumulate(a, target, n, defer=False)
+        else:
+            proj.store(a, target, n)
+
+
+@MIXERS.register("mingru")
+class MinGRU(_StatefulMixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden, self.width = int(self.params["hidden_size"]), int(self.params["width"])
+
+    def tensor_specs(self):
+        w, h = self.width, self.hidden
+        return {"z": TensorSpec((w, h)), "z.b": TensorSpec((w,), "vector", "normal"),
+                "x": TensorSpec((w, h)), "x.b": TensorSpec((w,), "vector", "normal"),
+                "g": TensorSpec((w, h)), "o": TensorSpec((h, w))}
+
+    def fused_tensors(self):
+        return {"zxg": ("z", "x", "g")}          # one product for the three projections
+
+    def state_need(self):
+        return StateNeed((self.width,), torch.float32)
+
+    def workspace(self):
+        return {f"mingru_p_{self.width}": (3 * self.width, "f32"), f"mingru_s_{self.width}": (self.width, "act")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        fused = tensors.get("zxg")
+        if fused is None:
+            fused = torch.cat([tensors["z"], tensors["x"], tensors["g"]], dim=0).contiguous()
+        self.zxg = Linear(fused, rt)
+        self.o = Linear(tensors["o"], rt)
+        self.bz, self.bx = tensors["z.b"], tensors["x.b"]
+
+    def _run(self, ctx, h, target, view, accumulate):
+        n, w = ctx.n_tokens, self.width
+        p = ctx.buf(f"mingru_p_{w}", 3 * w, torch.float32)
+        s = ctx.buf(f"mingru_s_{w}", w)
+        self.zxg.store(h, p, n)
+        ops.mingru_scan(p, self.bz, self.bx, ctx.seq_start, ctx.seq_slot, view.state, s, ctx.n_seqs, w)
+        self._finish(self.o, s, target, n, accumulate)
+
+    def resident_tensors(self):
+        return [self.zxg.w, self.o.w, self.bz, self.bx]
+
+
+@MIXERS.register("mamba2")
+class Mamba2(_StatefulMixer):
+    MAX_STATE, MAX_TAPS = 256, 16          # the scan kernel's and the convolution kernel's limits
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.vdim, self.n_state = int(p["heads"]), int(p["vdim"]), int(p["state"])
+        self.groups, self.norm_groups, self.taps = int(p["groups"]), int(p["norm_groups"]), int(p["conv"])
+        self.eps = float(p["eps"])
+        self.inner = self.heads * self.vdim
+        self.channels = self.inner + 2 * self.groups * self.n_state          # what the convolution sees
+        self.proj_width = 2 * self.inner + 2 * self.groups * self.n_state + self.heads
+        if self.heads % self.groups:
+            raise ValueError(f"{self.heads} heads do not divide over {self.groups} groups")
+        if self.inner % self.norm_groups:
+            raise ValueError(f"{self.inner} columns do not divide into {self.norm_groups} norm parts")
+        self.state_floats = self.heads * self.n_state * self.vdim
+        self.conv_floats = (self.taps - 1) * self.channels
+
+    def check_limits(self, rt):
+        if self.n_state > self.MAX_STATE:
+            raise ValueError(f"state size {self.n_state} is beyond the scan kernel's limit of {self.MAX_STATE}")
+        if not 1 <= self.taps <= self.MAX_TAPS:
+            raise ValueError(f"a convolution of {self.taps} taps is outside the kernel's 1..{self.MAX_TAPS}")
+
+    def tensor_specs(self):
+        return {"in": TensorSpec((self.proj_width, self.hidden)),
+                "conv": TensorSpec((self.channels, self.taps)),
+                "conv.b": TensorSpec((self.channels,), "vector", "normal"),
+                "dt_bias": TensorSpec((self.heads,), "vector", "normal"),
+                "A_log": TensorSpec((self.heads,), "vector", "normal"),
+                "D": TensorSpec((self.heads,), "vector", "ones"),
+                "norm": TensorSpec((self.inner,), "vector"),
+                "o": TensorSpec((self.hidden, self.inner))}
+
+    def state_need(self):
+        return StateNeed((self.state_floats + self.conv_floats,), torch.float32)
+
+    def _names(self):
+        tag = f"{self.proj_width}_{self.inner}"
+        return f"mamba_proj_{tag}", f"mamba_conv_{tag}", f"mamba_y_{tag}", f"mamba_g_{tag}"
+
+    def workspace(self):
+        proj, conv, y, g = self._names()
+        return {proj: (self.proj_width, "f32"), conv: (self.channels, "f32"), y: (self.inner, "f32"),
+                g: (self.inner, "act")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_in = Linear(tensors["in"], rt)
+        self.o = Linear(tensors["o"], rt)
+        self.conv_w, self.conv_b = tensors["conv"], tensors["conv.b"]
+        self.dt_bias, self.a_log, self.d, self.norm = tensors["dt_bias"], tensors["A_log"], tensors["D"], tensors["norm"]
+
+    def _run(self, ctx, h, target, view, accumulate):
+        n = ctx.n_tokens
+        names = self._names()
+        proj = ctx.buf(names[0], self.proj_width, torch.float32)
+        conv = ctx.buf(names[1], self.channels, torch.float32)
+        y = ctx.buf(names[2], self.inner, torch.float32)
+        g = ctx.buf(names[3], self.inner)
+        ssm_state = view.state[:, :self.state_floats]
+        conv_state = view.state[:, self.state_floats:self.state_floats + self.conv_floats]
+        self.w_in.store(h, proj, n)
+        ops.causal_conv_silu(proj, self.inner, self.conv_w, self.conv_b, self.taps, self.channels, ctx.tok_seq,
+                             ctx.seq_start, ctx.seq_slot, conv_state, conv, n, ctx.n_seqs)
+        ops.mamba2_scan(conv, proj, self.proj_width - self.heads, self.dt_bias, self.a_log, self.d, ctx.seq_start,
+                        ctx.seq_slot, ssm_state, y, ctx.n_seqs, self.heads, self.vdim, self.n_state, self.groups)
+        ops.gated_group_rmsnorm(y, proj[:, :self.inner], self.norm, g, n, self.norm_groups, self.eps)
+        self._finish(self.o, g, target, n, accumulate)
+
+    def resident_tensors(self):
+        return [self.w_in.w, self.o.w, self.conv_w, self.conv_b, self.dt_bias, self.a_log, self.d, self.norm]

@@ -3,7 +3,8 @@
 One registry maps an architecture name (config.json `architectures[0]` or
 `model_type`) to its configuration class and model description; four more map
 the kinds of parts (mixer, feed-forward, norm, position encoding, block
-arrangement) to their classes.  Unknown names are rejected with the list of
+arrangement, auxiliary parts of an arrangement, junctions between layers) to
+their classes.  Unknown names are rejected with the list of
 registered ones; nothing is approximated (the reference's rule for unknown
 `general.architecture`, src/model.rs:157-168, src/model/preflight.rs:31-43).
 """
@@ -60,3 +61,5 @@ POSITIONS: Registry = Registry("position encoding")
 BLOCKS: Registry = Registry("block arrangement")
 EMBEDDINGS: Registry = Registry("embedding")
 HEADS: Registry = Registry("output head")
+AUXILIARIES: Registry = Registry("auxiliary part")     # parts an arrangement names in `LayerSpec.extras` (a token shift, a gate)
+JUNCTIONS: Registry = Registry("junction")             # parts that act on the residual stream between two layers

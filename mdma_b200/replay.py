@@ -39,15 +39,18 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     page = 64
     max_tokens = -(-args.max_tokens // page) * page
-    probe_cfg = json.load(open(os.path.join(args.model, "config.json")))
-    max_context = min(int(probe_cfg.get("max_position_embeddings", max_tokens)), max_tokens)
+    # the model class and its sizes come from config.json through the architecture registry, as for generation
+    from mdma_b200.config import load_config
+    arch, config = load_config(args.model)
+    spec = arch.describe(config)
+    max_context = min(int(spec.max_positions), max_tokens)
     extra = {} if args.chunk_tokens is None else {"chunk_tokens": args.chunk_tokens}
     # A step may want the logits of every token it brings, so the logits buffer has a row per token of the
     # cache; but never more than a quarter of the free device memory (a step that wants more rows than
     # that is refused with the engine's own error, not truncated).
     import torch
     logit_rows = max_tokens
-    vocab = int(probe_cfg.get("vocab_size", 0))
+    vocab = int(spec.vocab_size)
     if vocab > 0 and torch.cuda.is_available():
         free_bytes, _ = torch.cuda.mem_get_info()
         logit_rows = max(64, min(max_tokens, (free_bytes // 4) // (4 * vocab)))

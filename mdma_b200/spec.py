@@ -47,8 +47,8 @@ class LayerSpec:
     block: str
     mixer_norm: PartSpec
     mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    ffn_norm: Optional[PartSpec]          # None with `ffn`: a layer without a feed-forward
+    ffn: Optional[PartSpec]
     extras: dict[str, PartSpec] = field(default_factory=dict)
 
 
@@ -59,6 +59,10 @@ class ScheduleEntry:
     cache reads it and writes nothing."""
     layer: int
     cache: Optional[int] = None
+    # a junction (index into `ModelSpec.junctions`) that acts on the residual stream right before
+    # this run, and the number it is given (which pass of a loop begins here)
+    junction: Optional[int] = None
+    junction_arg: int = 0
 
 
 @dataclass
@@ -72,3 +76,4 @@ class ModelSpec:
     final_norm: PartSpec
     lm_head: PartSpec
     stop_token_ids: tuple = ()
+    junctions: list[PartSpec] = field(default_factory=list)
