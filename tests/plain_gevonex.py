@@ -145,5 +145,5 @@ def forward(cfg, W, ids, trace=None):
             trace.append(x.clone())
     h = dyt(x, W["final.norm"], W["final.norm.b"], W["final.norm.alpha"])
     logits = h @ W["head"].t()
-    cap = cfg["logit_softcap"]
-    return cap * torch.tanh(logits / cap)
+    cap = cfg.get("logit_softcap")
+    return cap * torch.tanh(logits / cap) if cap else logits

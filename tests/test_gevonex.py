@@ -1,0 +1,511 @@
+"""The Gevonex architecture against its plain statement (tests/plain_gevonex.py): every
+mechanism alone through its kernel, then whole models through the engine's step function,
+the cache and state manager, the scheduler and the generation loop.  Configurations and
+weights are made here (tests/gevonex_tiny.py)."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gevonex as pg
+from gevonex_tiny import CFG_A, CFG_B, CFG_C, make_model, make_tensors
+
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+# float32: absolute, against the float64 statement.  bfloat16: absolute, and a row's root-mean-square error as a
+# share of the row's own deviation; on a B200 the largest seen over these models were 0.09 and 2.5 %.
+TOL = {"float32": 2e-4, "bfloat16": 0.25}
+TOL_ROW_BF16 = 0.06
+
+
+def ids_of(cfg, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, cfg["vocab"], (n,), generator=g).tolist()
+
+
+_largest = {}        # the largest errors seen, printed at exit when GEVONEX_TEST_REPORT is set
+
+
+def close(got, ref, dtype, what=""):
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    assert np.isfinite(got).all(), f"{what}: logits that are not finite"
+    err = np.abs(got - ref)
+    _largest[dtype] = max(_largest.get(dtype, 0.0), float(err.max()))
+    assert err.max() < TOL[dtype], f"{what}: {err.max()}"
+    if dtype == "bfloat16" and ref.ndim == 2:
+        rel = np.sqrt((err ** 2).mean(axis=-1)) / ref.std(axis=-1)
+        _largest["row"] = max(_largest.get("row", 0.0), float(rel.max()))
+        assert rel.max() < TOL_ROW_BF16, f"{what}: row error {rel.max()} of the row's deviation"
+
+
+if os.environ.get("GEVONEX_TEST_REPORT"):
+    import atexit
+    atexit.register(lambda: print("largest errors seen:", _largest))
+
+
+# =====================================================================================================
+# Without a GPU: configuration, description, and that the plain statement itself notices each mechanism.
+
+def test_config_is_read_and_checked():
+    from mdma_b200.config import ConfigError, load_config
+    arch, c = load_config(CFG_A)
+    assert arch.name == "Gevonex" and c.width == 64 and c.loop_times == 3 and c.layers[1].mlp is None
+    spec = arch.describe(c)
+    runs = [(e.layer, e.junction, e.junction_arg) for e in spec.schedule]
+    assert runs == [(0, None, 0), (1, 0, 0), (2, None, 0), (1, 0, 1), (2, None, 0), (1, 0, 2), (2, None, 0), (3, None, 0)]
+    assert [(i, t) for i, t in pg.layer_runs(CFG_A)] == [(l, a if j is not None else None) for l, j, a in runs]
+    _, b = load_config(CFG_B)
+    assert b.loop_times == 0 and b.logit_softcap == 0.0 and not arch.describe(b).junctions
+    for breaker in (lambda d: d.pop("width"), lambda d: d.update(extra_key=1),
+                    lambda d: d["layers"][0].update(type="lstm"),
+                    lambda d: d["layers"][0]["mixer"].pop("groups"),
+                    lambda d: d["layers"][0]["mlp"].update(kind="routed"),
+                    lambda d: d["loop"].update(stop=9), lambda d: d["loop"].update(times=0),
+                    lambda d: d["layers"][0]["mixer"].update(groups=3)):
+        bad = json.loads(json.dumps(CFG_A))
+        breaker(bad)
+        with pytest.raises(ConfigError):
+            load_config(bad)
+
+
+def test_tensor_inventory_and_plan_without_a_device(tmp_path):
+    from mdma_b200.config import load_config
+    from mdma_b200.engine.model import DecoderModel
+    from mdma_b200.engine.step import plan_only
+    arch, c = load_config(CFG_A)
+    model = DecoderModel(arch.describe(c))
+    names = set(model.expected_tensors())
+    assert {"embed", "head", "final.norm", "final.norm.b", "final.norm.alpha", "loop.in", "loop.step", "l0.shift",
+            "l0.rg1", "l0.rg1.b", "l0.rg2.b", "l0.mix.A_log", "l1.mix.sink", "l1.mix.dkv.norm", "l2.mix.z.b"} <= names
+    assert "l1.rg2" not in names and "l1.norm2" not in names and "l1.mlp.up" not in names     # no feed-forward there
+    # every run of a looped layer owns its state and its cache
+    assert len(model.state_needs()) == 8 and all(n is not None for n in model.state_needs())
+    kv = model.kv_needs()
+    assert [n is not None for n in kv] == [False, True, False, True, False, True, False, True]
+    assert kv[1].head_dim == 40 and kv[1].n_kv_heads == 1 and not kv[1].values and kv[7].head_dim == 16
+    d, _ = make_model(CFG_A, 3, root=str(tmp_path))
+    plan = plan_only(d, dtype="float32", max_batch=2, max_context=128)
+    assert plan["total_bytes"] > 0 and plan["cache_bytes"] > 0
+
+
+def test_the_plain_statement_notices_each_mechanism():
+    """Leaving a mechanism out of the plain statement moves the logits by far more than any tolerance here."""
+    W = make_tensors(CFG_A, 5)
+    ids = ids_of(CFG_A, 40, 1)
+    ref = pg.forward(CFG_A, W, ids)
+
+    def moved(changes):
+        W2 = dict(W)
+        W2.update(changes)
+        return float((pg.forward(CFG_A, W2, ids) - ref).abs().max())
+    assert moved({"l1.mix.sink": W["l1.mix.sink"] - 30.0}) > 0.05                  # no sink
+    assert moved({"l2.shift": torch.zeros_like(W["l2.shift"])}) > 0.05             # no token shift
+    assert moved({"loop.step": torch.zeros_like(W["loop.step"])}) > 0.05           # passes not told apart
+    assert moved({"l0.rg1.b": W["l0.rg1.b"] + 30.0}) > 0.05                        # gate always open
+    conv = W["l0.mix.conv"].clone()
+    conv[:, :-1] = 0
+    assert moved({"l0.mix.conv": conv}) > 0.05                                     # no taps back
+    assert moved({"l0.mix.A_log": W["l0.mix.A_log"] + 6.0}) > 0.02                 # a state that forgets at once
+    assert moved({"l0.norm1.alpha": W["l0.norm1.alpha"] * 0.5}) > 0.05
+
+
+# =====================================================================================================
+# Kernels alone (GPU).
+
+def _dev(t, dtype=torch.float32):
+    return t.to(device="cuda", dtype=dtype).contiguous()
+
+
+def _meta(lengths, slots):
+    starts = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    tok_seq = np.concatenate([np.full(n, s, dtype=np.int32) for s, n in enumerate(lengths)])
+    i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device="cuda")
+    return i32(tok_seq), i32(starts), i32(slots)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dyt_shift_and_gate_kernels(dtype):
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    W, lengths, slots = 72, [5, 1, 9], [4, 0, 2]
+    T = sum(lengths)
+    w, b, mu = 1 + 0.3 * torch.randn(W, generator=g), 0.2 * torch.randn(W, generator=g), torch.rand(W, generator=g)
+    alpha = torch.tensor(0.7)
+    state = torch.zeros(6, W + 5, device="cuda")          # rows wider than the part's own: a view is handed out
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    # two steps of the same three sequences: the second reads what the first left
+    xs = [torch.randn(T, W, generator=g) * 2 for _ in range(2)]
+    whole = {s: torch.cat([x[sum(lengths[:s]):sum(lengths[:s + 1])] for x in xs]).double() for s in range(3)}
+    for step, x in enumerate(xs):
+        tok_seq, seq_start, seq_slot = _meta(lengths, slots)
+        h, hs = torch.empty(T, W, device="cuda", dtype=dtype), torch.empty(T, W, device="cuda", dtype=dtype)
+        h2, hs2 = torch.empty_like(h), torch.empty_like(h)
+        vec = [_dev(v, dtype) for v in (w, b, alpha, mu)]
+        ops.dyt_shift(_dev(x), *vec, tok_seq, seq_start, seq_slot, state[:, :W], h, hs, T)
+        ops.dyt_norm(_dev(x), *vec[:3], h2)
+        ops.token_shift(h2, vec[3], tok_seq, seq_start, seq_slot, state[:, :W], hs2, T)
+        assert torch.equal(h, h2) and torch.equal(hs, hs2)             # fused and separate: the same numbers
+        for s in range(3):
+            full = pg.token_shift(pg.dyt(whole[s], w.double(), b.double(), alpha.double()), mu.double())
+            lo = step * lengths[s]
+            rows = slice(sum(lengths[:s]), sum(lengths[:s + 1]))
+            assert (hs[rows].double().cpu() - full[lo:lo + lengths[s]]).abs().max() < tol, (step, s)
+        # the gated add, which also keeps each sequence's last normed row
+        xr, y, gate = torch.randn(T, W, device="cuda"), torch.randn(T, W, device="cuda"), torch.randn(T, W, device="cuda").to(dtype)
+        want = xr + torch.sigmoid(gate.float()) * y
+        ops.gated_add(xr, gate, y, T, h, tok_seq, seq_start, seq_slot, state[:, :W])
+        assert (xr - want).abs().max() < 1e-5
+        for s in range(3):
+            assert torch.equal(state[slots[s], :W], h[sum(lengths[:s + 1]) - 1].float())
+        assert float(state[:, W:].abs().max()) == 0 and float(state[[1, 3, 5]].abs().max()) == 0      # nobody else's rows
+
+
+@pytest.mark.gpu
+def test_mingru_and_convolution_in_portions():
+    """The recurrence and the short convolution over a sequence cut in portions of 1, 2, 7, ... equal the plain run."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    Wd, taps, C = 40, 4, 24
+    total, cuts = 37, [1, 2, 7, 1, 1, 20, 5]
+    p = torch.randn(total, 3 * Wd, generator=g)
+    bz, bu = torch.randn(Wd, generator=g), torch.randn(Wd, generator=g)
+    z = torch.sigmoid(p[:, :Wd].double() + bz.double())
+    u = p[:, Wd:2 * Wd].double() + bu.double()
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    S, want = torch.zeros(Wd, dtype=torch.float64), []
+    for t in range(total):
+        S = (1 - z[t]) * S + z[t] * cand[t]
+        want.append(S * pg.silu(p[t, 2 * Wd:].double()))
+    want = torch.stack(want)
+    proj = torch.randn(total, 10 + C, generator=g)
+    cw, cb = torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
+    conv_want = pg.silu(pg.causal_conv(proj[:, 10:].double(), cw.double(), cb.double()))
+    state = torch.zeros(3, Wd, device="cuda")
+    cstate = torch.zeros(3, (taps - 1) * C, device="cuda")
+    got, conv_got, at = [], [], 0
+    for n in cuts:
+        tok_seq, seq_start, seq_slot = _meta([n], [2])
+        out = torch.empty(n, Wd, device="cuda")
+        ops.mingru_scan(_dev(p[at:at + n]), _dev(bz), _dev(bu), seq_start, seq_slot, state, out, 1, Wd)
+        got.append(out.cpu())
+        co = torch.empty(n, C, device="cuda")
+        ops.causal_conv_silu(_dev(proj[at:at + n]), 10, _dev(cw), _dev(cb), taps, C, tok_seq, seq_start, seq_slot,
+                             cstate, co, n, 1)
+        conv_got.append(co.cpu())
+        at += n
+    assert (torch.cat(got).double() - want).abs().max() < 1e-5
+    assert (torch.cat(conv_got).double() - conv_want).abs().max() < 1e-5
+    assert float(state[:2].abs().max()) == 0 and float(cstate[:2].abs().max()) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,vdim,N,G", [(4, 8, 16, 2), (3, 40, 24, 3), (2, 20, 72, 1), (6, 5, 200, 2), (1, 130, 4, 1)])
+def test_mamba2_scan_shapes_and_portions(heads, vdim, N, G):
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(N)
+    inner, lengths, slots = heads * vdim, [19, 3], [1, 3]
+    conv = torch.randn(2, 44, inner + 2 * G * N, generator=g) * 0.7           # two sequences, 44 rows each in all
+    raw = torch.randn(2, 44, heads + 3, generator=g)
+    dt_bias, a_log, D = torch.rand(heads, generator=g) * 3 - 3, torch.rand(heads, generator=g) * 2 - 1, torch.randn(heads, generator=g)
+    want = []
+    for s in range(2):
+        dt = torch.nn.functional.softplus(raw[s, :, 3:].double() + dt_bias.double(), threshold=1e9)
+        x = conv[s, :, :inner].double().reshape(-1, heads, vdim)
+        B = conv[s, :, inner:inner + G * N].double().reshape(-1, G, N)
+        C = conv[s, :, inner + G * N:].double().reshape(-1, G, N)
+        S = torch.zeros(heads, N, vdim, dtype=torch.float64)
+        y = torch.zeros(44, heads, vdim, dtype=torch.float64)
+        for t in range(44):
+            for h in range(heads):
+                gi = h // (heads // G)
+                S[h] = torch.exp(-torch.exp(a_log[h].double()) * dt[t, h]) * S[h] + dt[t, h] * torch.outer(B[t, gi], x[t, h])
+                y[t, h] = S[h].t() @ C[t, gi] + D[h].double() * x[t, h]
+        want.append(y.reshape(44, inner))
+    state = torch.zeros(4, heads * N * vdim + 7, device="cuda")
+    # step 1: 19 and 3 rows; step 2: the rest of both, sequences in the other order
+    got = [[], []]
+    for order, take in (([0, 1], lengths), ([1, 0], [44 - lengths[1], 44 - lengths[0]])):
+        lo = [0 if not got[s] else lengths[s] for s in order]
+        rows_c = torch.cat([conv[s, l:l + n] for s, l, n in zip(order, lo, take)])
+        rows_r = torch.cat([raw[s, l:l + n] for s, l, n in zip(order, lo, take)])
+        _, seq_start, seq_slot = _meta(take, [slots[s] for s in order])
+        y = torch.empty(sum(take), inner, device="cuda")
+        ops.mamba2_scan(_dev(rows_c), _dev(rows_r), 3, _dev(dt_bias), _dev(a_log), _dev(D), seq_start, seq_slot,
+                        state[:, :heads * N * vdim], y, 2, heads, vdim, N, G)
+        at = 0
+        for s, n in zip(order, take):
+            got[s].append(y[at:at + n].cpu())
+            at += n
+    for s in range(2):
+        assert (torch.cat(got[s]).double() - want[s]).abs().max() < 2e-4, s
+    assert float(state[[0, 2]].abs().max()) == 0 and float(state[:, heads * N * vdim:].abs().max()) == 0
+
+
+@pytest.mark.gpu
+def test_gated_group_norm_softcap_pack_and_headwise_product():
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    T, width, parts = 7, 60, 3
+    y, zz, w = torch.randn(T, width, generator=g), torch.randn(T, width + 9, generator=g), 1 + 0.2 * torch.randn(width, generator=g)
+    out = torch.empty(T, width, device="cuda")
+    ops.gated_group_rmsnorm(_dev(y), _dev(zz)[:, 4:4 + width], _dev(w), out, T, parts, 1e-5)
+    v = y.double() * pg.silu(zz[:, 4:4 + width].double())
+    want = pg.rms_unit(v.reshape(T, parts, -1), 1e-5).reshape(T, width) * w.double()
+    assert (out.cpu().double() - want).abs().max() < 1e-5
+    lg = _dev(torch.randn(5, 33, generator=g) * 20)
+    ref = 11.0 * torch.tanh(lg.double() / 11.0)
+    ops.softcap(lg, 5, 11.0)
+    assert (lg.double() - ref).abs().max() < 1e-5
+    a, b2 = torch.randn(T, 10, generator=g), torch.randn(T, 10, generator=g)
+    pair = torch.empty(T, 20, device="cuda", dtype=torch.bfloat16)
+    ops.pack_pair(_dev(a), _dev(b2), pair, T)
+    assert torch.equal(pair.cpu(), torch.cat([a, b2], 1).to(torch.bfloat16))
+    heads, n, k = 3, 10, 6
+    a, wh = torch.randn(T, heads * k + 5, generator=g), torch.randn(heads, n, k, generator=g)
+    out = torch.zeros(T, heads * n, device="cuda")
+    ops.gemm_simt_batched(_dev(a), _dev(wh), out, T)
+    want = torch.einsum("thk,hnk->thn", a[:, :heads * k].reshape(T, heads, k).double(), wh.double()).reshape(T, -1)
+    assert (out.cpu().double() - want).abs().max() < 1e-5
+
+
+def _plain_latent_scores(q_lat, c, sink, scale, window):
+    """q_lat [T, H, R] at positions 0..T-1 over latents c [T, R]; returns the weighted sums [T, H, R]."""
+    T, H, R = q_lat.shape
+    out = torch.zeros(T, H, R, dtype=torch.float64)
+    for t in range(T):
+        lo = max(0, t + 1 - window) if window else 0
+        for h in range(H):
+            s = (c[lo:t + 1] @ q_lat[t, h]) * scale
+            top = max(float(s.max()), float(sink[h]))
+            e = torch.exp(s - top)
+            out[t, h] = (e / (e.sum() + math.exp(float(sink[h]) - top))) @ c[lo:t + 1]
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 17])
+def test_latent_attention_kernel_sink_window_far_key_and_pages(dtype, window):
+    """A cache of scattered 16-row pages.  One far key (position 3) is made to stand out for the last query's
+    head 1; with a window it must be invisible, and the keys at the window's two edges are told apart."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    T, H, R, page, scale = 150, 3, 40, 16, 0.3
+    c = torch.randn(T, R, generator=g).to(dtype).double()
+    q = torch.randn(T, H, R, generator=g) * 0.5
+    q[T - 1, 1] = 6.0 * c[3].float() / c[3].norm().float()          # asks for the far key
+    if window:
+        q[T - 2, 0] = 6.0 * c[T - 1 - window].float() / c[T - 1 - window].norm().float()   # first key inside its window
+        q[T - 1, 0] = 6.0 * c[T - 1 - window].float() / c[T - 1 - window].norm().float()   # the same key, now just outside
+    q = q.to(dtype).double()
+    sink = torch.tensor([0.5, -1.0, 3.0])
+    n_pages, max_pages = 40, 12
+    perm = torch.randperm(n_pages, generator=g)[:max_pages].to(torch.int32)
+    cache = torch.full((n_pages, page, 1, R), float("nan"), dtype=dtype)
+    for t in range(T):
+        cache[perm[t // page], t % page, 0] = c[t].to(dtype)
+    table = torch.zeros(5, max_pages, dtype=torch.int32)
+    table[2] = perm
+    i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device="cuda")
+    out = torch.empty(T, H * R, device="cuda", dtype=dtype)
+    ops.latent_attention(_dev(q.reshape(T, H * R), dtype), cache.cuda(), _dev(sink), i32([0] * T), i32(range(T)), i32([2]),
+                         table.cuda(), max_pages, page, out, T, H, R, window, scale)
+    want = _plain_latent_scores(q, c, sink.double(), scale, window)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    got = out.double().cpu().reshape(T, H, R)
+    assert (got - want).abs().max() < tol
+    if not window:      # the far key carries the last query's head 1: the result is close to that latent
+        assert (want[T - 1, 1] - c[3]).abs().max() < 0.05 * c[3].abs().max()
+    else:               # the edge key is seen from T-2 and not from T-1
+        edge = c[T - 1 - window]
+        assert (want[T - 2, 0] - edge).abs().max() < 0.05 * edge.abs().max()
+        assert (want[T - 1, 0] - edge).abs().max() > 0.3 * edge.abs().max()
+
+
+# =====================================================================================================
+# Whole models through the engine (GPU).
+
+_models: dict = {}
+
+
+def model_of(key, dtype):
+    """(folder, config, float64-ready tensors as the engine holds them) of configuration `key`."""
+    k = (key, dtype)
+    if k not in _models:
+        store = torch.float32 if dtype == "float32" else torch.bfloat16
+        d, W = make_model(CONFIGS[key], 11 + ord(key), store)
+        _models[k] = (d, CONFIGS[key], W)
+    return _models[k]
+
+
+_refs: dict = {}
+
+
+def ref_of(key, dtype, ids):
+    k = (key, dtype, tuple(ids))
+    if k not in _refs:
+        _, cfg, W = model_of(key, dtype)
+        _refs[k] = pg.forward(cfg, W, ids).numpy()
+    return _refs[k]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
+def test_every_layer_against_the_plain_statement(key, dtype):
+    """The residual stream after every run of a layer, then the logits; one short prompt."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of(key, dtype)
+    ids = ids_of(cfg, 21, 4)
+    trace = []
+    ref = pg.forward(cfg, W, ids, trace)
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=64, logit_rows=64, page_size=16)
+    got = []
+    eng.model.on_layer = lambda n, x: got.append(x.detach().double().cpu())
+    s = eng.acquire()
+    logits = eng.step([StepEntry(s, ids, list(range(len(ids))))]).cpu().numpy()
+    assert len(got) == len(trace)
+    tol = 1e-4 if dtype == "float32" else 0.02
+    for n, (a, b) in enumerate(zip(got, trace)):
+        assert (a - b).abs().max() < tol * max(1.0, float(b.abs().max())), f"after run {n} of the schedule"
+    close(logits, ref.numpy(), dtype, "logits")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
+def test_batches_portions_decoding_and_reuse(key, dtype):
+    """Unequal prompts in one step; the same prompts cut in portions down to one and two tokens on a cached
+    prefix; token-by-token decoding; sequences that end early while others go on; slots and pages freed and
+    taken again (rows nobody owns hold NaN throughout).  In float32 every way of cutting gives the same bits."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of(key, dtype)
+    lengths = [70, 1, 33, 2, 17]
+    seqs = [ids_of(cfg, n, 20 + i) for i, n in enumerate(lengths)]
+    refs = [ref_of(key, dtype, s) for s in seqs]
+    eng = Engine(d, dtype=dtype, max_batch=5, max_context=96, logit_rows=160, page_size=16)
+
+    def run(plan):
+        """plan: per sequence, the sizes of its portions.  All sequences advance together, one portion a step."""
+        slots = [eng.acquire() for _ in seqs]
+        rows = [[] for _ in seqs]
+        at = [0] * len(seqs)
+        for step in range(max(len(p) for p in plan)):
+            live = [i for i in range(len(seqs)) if step < len(plan[i])]
+            eng.cache.poison_unused()
+            out = eng.step([StepEntry(slots[i], seqs[i][at[i]:at[i] + plan[i][step]], list(range(plan[i][step])))
+                            for i in live]).cpu().numpy()
+            o = 0
+            for i in live:
+                n = plan[i][step]
+                rows[i].append(out[o:o + n].copy())
+                o += n
+                at[i] += n
+                if at[i] == len(seqs[i]):
+                    eng.release(slots[i])           # ends early; its slot and pages go back
+        eng.cache.check()
+        return [np.concatenate(r) for r in rows]
+
+    whole = run([[n] for n in lengths])
+    for i, (got, ref) in enumerate(zip(whole, refs)):
+        close(got, ref, dtype, f"whole prompts, sequence {i}")
+    alone = []
+    for i, s in enumerate(seqs):                    # each alone, in a slot that the batch used
+        slot = eng.acquire()
+        alone.append(eng.step([StepEntry(slot, s, list(range(len(s))))]).cpu().numpy().copy())
+        eng.release(slot)
+    pieces = run([[2, 1, 30, 17, 1, 2, 16, 1], [1], [16, 1, 15, 1], [1, 1], [3, 14]])
+    decoded = run([[40] + [1] * 30, [1], [1] * 33, [2], [16, 1]])
+    for name, other in (("alone", alone), ("portions", pieces), ("decoded", decoded)):
+        for i, (got, ref) in enumerate(zip(other, refs)):
+            close(got, ref, dtype, f"{name}, sequence {i}")
+            if dtype == "float32":
+                assert np.abs(got - whole[i]).max() <= 2e-6, f"{name}, sequence {i}: differs from the whole prompt"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_passes_smaller_than_a_step_and_long_decoding(dtype):
+    """A step run as passes of 7 tokens (cuts inside sequences), then 150 tokens decoded one by one across many
+    page borders, beside a batch mate that ends on the way and whose slot another request takes."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of("A", dtype)
+    long_ids, mate, late = ids_of(cfg, 190, 31), ids_of(cfg, 60, 32), ids_of(cfg, 25, 33)
+    r_long, r_mate, r_late = (ref_of("A", dtype, s) for s in (long_ids, mate, late))
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=192, logit_rows=64, page_size=16, chunk_tokens=7)
+    a, b = eng.acquire(), eng.acquire()
+    out = eng.step([StepEntry(a, long_ids[:40], [0, 39, 6, 7]), StepEntry(b, mate[:41], [40, 13])]).cpu().numpy()
+    assert eng.forward_passes > 10
+    close(out, np.stack([r_long[0], r_long[39], r_long[6], r_long[7], r_mate[40], r_mate[13]]), dtype, "passes")
+    pb = 41
+    for p in range(40, 190):
+        entries = [StepEntry(a, [long_ids[p]], [0])]
+        second = None
+        if pb < len(mate):
+            entries.append(StepEntry(b, [mate[pb]], [0]))
+            second = r_mate[pb]
+            pb += 1
+        elif pb == len(mate):                       # the mate is done: its slot goes to a late request
+            eng.release(b)
+            b = eng.acquire()
+            entries.append(StepEntry(b, late, [len(late) - 1]))
+            second = r_late[-1]
+            pb += 1
+        eng.cache.poison_unused()
+        out = eng.step(entries).cpu().numpy()
+        close(out[0], r_long[p], dtype, f"decoded position {p}")
+        if second is not None:
+            close(out[1], second, dtype, f"batch mate at step {p}")
+    eng.cache.check()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("key", ["A", "C"])
+def test_greedy_generation_through_the_scheduler(key):
+    """`Engine.generate`: batches, the decode session's replayed graphs, argmax.  float32 tokens equal the plain
+    statement's greedy continuation; replayed and step-by-step runs give the same tokens in both dtypes."""
+    from mdma_b200.engine import Engine
+    d, cfg, W = model_of(key, "float32")
+    prompts = [ids_of(cfg, n, 40 + n) for n in (9, 30, 3)]
+    want = []
+    for p in prompts:
+        ids = list(p)
+        for _ in range(12):
+            ids.append(int(pg.forward(cfg, W, ids)[-1].argmax()))
+        want.append(ids[len(p):])
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=64)            # three requests, two slots: two batches
+    assert eng.decode_session().graph_safe
+    for graphs in (True, False):
+        outs = eng.generate(prompts, max_tokens=12, use_graphs=graphs)
+        assert [o.tokens for o in outs] == want, graphs
+    d16, _, _ = model_of(key, "bfloat16")
+    eng = Engine(d16, dtype="bfloat16", max_batch=3, max_context=64)
+    a = eng.generate(prompts, max_tokens=12, use_graphs=True)
+    b = eng.generate(prompts, max_tokens=12, use_graphs=False)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
+    sampled = eng.generate(prompts, max_tokens=8, temperature=0.9, top_p=0.9, seed=3)
+    assert all(len(o.tokens) == 8 for o in sampled)
+
+
+@pytest.mark.gpu
+def test_trace_replay_and_command_line(tmp_path):
+    from replay_util import replay
+    d, cfg, W = model_of("B", "float32")
+    a, b = ids_of(cfg, 30, 50), ids_of(cfg, 11, 51)
+    ra, rb = ref_of("B", "float32", a), ref_of("B", "float32", b)
+    steps = [{"entries": [{"id": "a", "tokens": a[:20], "want": [0, 19]}, {"id": "b", "tokens": b[:9], "want": []}], "end": []},
+             {"entries": [{"id": "a", "tokens": [a[20]], "want": [0]}, {"id": "b", "tokens": [b[9]], "want": [0]}], "end": []},
+             {"entries": [{"id": "a", "tokens": [a[21]], "want": []}, {"id": "b", "tokens": [b[10]], "want": [0]}], "end": ["b"]},
+             {"entries": [{"id": "a", "tokens": a[22:], "want": [7]}], "end": ["a"]}]
+    out = replay(d, "float32", steps, 128, cfg["vocab"])
+    close(out[0], np.stack([ra[0], ra[19]]), "float32", "step 0")
+    close(out[1], np.stack([ra[20], rb[9]]), "float32", "step 1")
+    close(out[2], rb[10:11], "float32", "step 2")
+    close(out[3], ra[29:30], "float32", "step 3")
+    from mdma_b200.cli import main
+    assert main(["run", d, " ".join(map(str, a[:5])), "--max-tokens", "4", "--dtype", "float32", "--max-context", "64"]) == 0
+    assert main(["plan", d, "--ctx", "64"]) == 0
