@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
     python bench.py --shape llama-2-7b | llama-3.2-1b [--batch B] [--prompt-len P] [--prefill-tokens T]
+    python bench.py --compare gevonex [--compare-widths 1024,2048,4096] [--compare-layers 4]
 
 Prints ONE JSON line.  The default run has the layer sizes of the
 Llama-3.1-8B shape with random bfloat16 weights, a batch of 8 sequences
@@ -13,6 +14,12 @@ around exactly K steps; `e2e` is the same through the Python entry point
 (`Generator.generate`, host token lists in and out).  Decoding streams 15 GB
 of weights per step, far more than the 126 MB L2, so nothing is flushed
 between steps.
+
+`--compare gevonex` is another program: prefill and decode throughput of the
+Gevonex architecture (recurrent and latent-attention mixers, random weights)
+at a few layer sizes, beside a Llama of the same width, depth and vocabulary,
+each with the share of the measured peaks it reaches.  It prints one JSON line
+of its own; the default workload and its line are unchanged.
 """
 from __future__ import annotations
 
@@ -124,6 +131,110 @@ def decode_bytes(cfg, layers, batch, context, elem_bytes=2):
     return (2 * (body + head) + batch * context * kv_row) * elem_bytes // 2
 
 
+def gevonex_config(width: int, layers: int, vocab: int) -> dict:
+    """A Gevonex of `layers` layers (Mamba-2, latent attention, minGRU, Mamba-2, ...) whose sizes follow the width
+    the way released models of these mixers do: heads of 64, state 128, an inner width of 2 x width for Mamba-2;
+    heads of 128 and a latent of 128 for the attention; a feed-forward of 4 x width."""
+    kinds = ["mamba2", "latent_attention", "mingru", "mamba2"]
+    mixers = {"mamba2": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4},
+              "latent_attention": {"heads": width // 128, "dim": 128, "vdim": 128, "kv_rank": 128, "scale": 128 ** -0.5},
+              "mingru": {"width": width}}
+    return {"architecture": "Gevonex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "loop": {"start": 0, "stop": layers, "times": 1},
+            "layers": [{"type": kinds[i % 4], "mixer": mixers[kinds[i % 4]], "mlp": {"kind": "dense", "ff": 4 * width}}
+                       for i in range(layers)]}
+
+
+def llama_like(width: int, layers: int, vocab: int) -> dict:
+    """The closest existing model at equal size: the same width, depth and vocabulary, heads of 128 in groups of
+    four, a gated feed-forward of 8/3 x width (the same three-matrix parameter count as 4 x width ungated + gate)."""
+    heads = width // 128
+    return dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=layers, hidden_size=width,
+                num_attention_heads=heads, num_key_value_heads=max(1, heads // 4), head_dim=128,
+                intermediate_size=(8 * width // 3 + 255) // 256 * 256, vocab_size=vocab, rope_theta=500000.0,
+                rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def compare(args) -> int:
+    import gc
+    import torch
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.sampling import SamplingParams
+    hbm_gbs, bf16_tflops, peak_src, _ = peaks()
+    torch.cuda.set_device(0)
+    warmup = max(3, args.warmup)
+    vocab, T, prompt = 32000, args.prefill_tokens, args.prompt_len
+    gen = torch.Generator().manual_seed(0)
+    ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    def measure(cfg, batch):
+        eng = Engine(config=cfg, seed=0, dtype=args.dtype, max_batch=batch, max_context=max(T, prompt + 512))
+        matrix_bytes = 0
+        for name, ts in eng.model.expected_tensors().items():
+            if len(ts.shape) == 2 and "embed" not in name:
+                matrix_bytes += 2 * ts.shape[0] * ts.shape[1]
+        times = []
+        for i in range(warmup + 5):
+            s = eng.acquire()
+            p = ids(T)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([StepEntry(s, p, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.release(s)
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        ms_p = sorted(times)[len(times) // 2]
+        slots = [eng.acquire() for _ in range(batch)]
+        ps = [ids(prompt) for _ in range(batch)]
+        logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, ps)])
+        toks, _ = eng.sampler.sample(logits, SamplingParams.greedy(), list(range(batch)), [0] * batch)
+        sess = eng.decode_session()
+        sess.start(slots, toks)
+        for _ in range(warmup):
+            sess.run(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = max(8, args.steps // 2)
+        e0.record()
+        done = 0
+        while done < steps:
+            done += sess.run(min(sess.max_run, steps - done))
+        e1.record()
+        torch.cuda.synchronize()
+        ms_d = e0.elapsed_time(e1) / steps
+        launches = sess.launches_per_step
+        eng.check_status()
+        del sess, eng
+        gc.collect()
+        torch.cuda.empty_cache()
+        # the matrices are read once per decode step and used twice per token and parameter in prefill; the cache
+        # and the state are left out of both counts (at these sizes a few per cent), so the shares are lower bounds
+        return {"matrix_gb": round(matrix_bytes / 1e9, 3),
+                "prefill_tokens_per_s": round(T * 1000.0 / ms_p, 1), "prefill_ms": round(ms_p, 3),
+                "prefill_frac_of_bf16_peak": round(T * matrix_bytes / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4),
+                "decode_tokens_per_s": round(batch * 1000.0 / ms_d, 1), "decode_ms_per_step": round(ms_d, 4),
+                "decode_frac_of_hbm_peak": round(matrix_bytes / (ms_d * 1e-3) / 1e9 / hbm_gbs, 4),
+                "launches_per_decode_step": launches}
+
+    clock = ClockSampler()
+    clock.start()
+    rows = []
+    for width in [int(w) for w in args.compare_widths.split(",")]:
+        row = {"width": width, "layers": args.compare_layers, "vocab": vocab, "batch": args.batch}
+        row["gevonex"] = measure(gevonex_config(width, args.compare_layers, vocab), args.batch)
+        row["llama"] = measure(llama_like(width, args.compare_layers, vocab), args.batch)
+        rows.append(row)
+    print(json.dumps({"compare": "gevonex beside llama at equal width, depth and vocabulary", "dtype": args.dtype,
+                      "prefill_tokens": T, "decode_after_prompts_of": prompt, "peaks": peak_src,
+                      "hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops,
+                      "timing": "CUDA events, inputs larger than L2 from width 2048 on (no flush)",
+                      "sizes": rows, "clocks": clock.stop()}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,8 +254,14 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the true 32-bit engine (CUDA-core kernels), for the record; the headline is bfloat16")
+    ap.add_argument("--compare", default=None, choices=["gevonex"],
+                    help="another program: the named architecture beside a Llama of equal size (see the header)")
+    ap.add_argument("--compare-widths", default="1024,2048,4096")
+    ap.add_argument("--compare-layers", type=int, default=4)
     args = ap.parse_args()
 
+    if args.compare is not None and args.impl != "reference":
+        return compare(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "AliOsm/mdma is a Rust crate (Cargo.toml, no setup.py/pyproject.toml); pip cannot "

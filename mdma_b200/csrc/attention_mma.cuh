@@ -62,6 +62,9 @@ struct AttnParams {
     int n_heads, n_kv_heads, head_dim, group, tile_tokens, window, splits;
     float scale_log2;                               // scale * log2(e)
     int* status;                                    // optional device word, set non-zero if a wait ran out
+    // A softmax with a sink: 2^(sink_log2[head] - m) is added to every row's denominator once (a term with
+    // no key and no value; the entries are the learned numbers times log2(e)).  Null: an ordinary softmax.
+    const float* sink_log2;
     // Decode with the rotary encoding done here (`rot_inv_freq` not null): the step's projection rows are
     // `q` (bfloat16, not yet rotated) or, with `proj_splits` > 0, the sum of that many float partial rows
     // [split][token][proj_width]; the block rotates its query heads and its key head, rounds them to
@@ -242,7 +245,7 @@ attention_mma_kernel(const AttnParams p) {
         const size_t token = (size_t)(row0_seq + tok0 + t);
         const int head = kvh * G + g;
         if (p.splits == 1) {
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / (p.sink_log2 ? l + exp2f(p.sink_log2[head] - m) : l);
             __nv_bfloat16* dst = p.out + (token * p.n_heads + head) * D;
 #pragma unroll
             for (int n = 0; n < DMAX / 8; ++n) {
@@ -465,6 +468,7 @@ attention_decode_kernel(const AttnParams p) {
         }
         const int head = kvh * G + r;
         if (p.splits == 1) {
+            if (p.sink_log2) l += exp2f(p.sink_log2[head] - m);
             p.out[((size_t)token * p.n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
         } else {
             const size_t slot = ((size_t)token * p.n_heads + head) * p.splits + split;
@@ -767,6 +771,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         const int head = kvh * G + r;
         if (p.splits == 1) {
+            if (p.sink_log2) l += exp2f(p.sink_log2[head] - m);
             p.out[((size_t)token * p.n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
         } else {
             const size_t slot = ((size_t)token * p.n_heads + head) * p.splits + split;
@@ -779,7 +784,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
 // out[token, head, :] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, splits taken in order.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
+                                       __nv_bfloat16* __restrict__ out, int splits, int head_dim,
+                                       const float* __restrict__ sink_log2, int n_heads) {
     chain_release();
     chain_wait();
     const size_t th = blockIdx.x;                   // token * heads + head
@@ -788,6 +794,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[s * 2]);
     float l = 0.f;
     for (int s = 0; s < splits; ++s) if (ml[s * 2] != -INFINITY) l += exp2f(ml[s * 2] - m) * ml[s * 2 + 1];
+    if (sink_log2) l += exp2f(sink_log2[th % n_heads] - m);          // the sink counts once, whatever the split
     const float inv = 1.0f / l;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float acc = 0.f;
@@ -856,7 +863,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
                        int max_pages, int page_size, void* out, int n_tokens, int n_seqs, int max_new,
                        int n_heads, int n_kv_heads, int head_dim, int window, float scale, int splits,
                        float* scratch, long scratch_floats, cudaStream_t stream, int n_pages = 0,
-                       int* status = nullptr, const FusedRotary* fz = nullptr) {
+                       int* status = nullptr, const FusedRotary* fz = nullptr, const float* sink_log2 = nullptr) {
     MDMA_REQUIRE(attention_mma_supported(n_heads, n_kv_heads, head_dim),
                  "attention_mma: heads %d / kv heads %d / head_dim %d is outside its limits (head_dim a multiple of 16 up to 128, group up to 64)",
                  n_heads, n_kv_heads, head_dim);
@@ -874,7 +881,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.group = n_heads / n_kv_heads; p.tile_tokens = kRows / p.group; p.window = window; p.splits = splits;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_o = nullptr; p.part_ml = nullptr; p.status = status;
+    p.part_o = nullptr; p.part_ml = nullptr; p.status = status; p.sink_log2 = sink_log2;
     p.rot_inv_freq = nullptr; p.rotary_dim = 0; p.rot_interleaved = 0;
     p.proj_partial = nullptr; p.proj_splits = 0; p.proj_split_stride = 0; p.proj_width = 0;
     p.k_cache_w = nullptr; p.v_cache_w = nullptr;
@@ -967,7 +974,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     }
     MDMA_LAUNCH_OK("attention_mma");
     if (splits > 1) {
-        launch_chained(attention_merge_kernel, dim3(n_tokens * n_heads), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, splits, head_dim);
+        launch_chained(attention_merge_kernel, dim3(n_tokens * n_heads), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, splits, head_dim, p.sink_log2, n_heads);
         MDMA_LAUNCH_OK("attention_merge");
     }
     return 0;

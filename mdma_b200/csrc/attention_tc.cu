@@ -41,6 +41,7 @@ struct AttnTcParams {
     int n_heads, n_kv_heads, head_dim, group, tile_tokens, window, n_tokens;
     float scale_log2;
     int* status;
+    const float* sink_log2;       // [n_heads] or null: 2^(sink_log2[head] - reference) joins the row's denominator once
 };
 
 // shared memory map (bytes), all tiles 1024-aligned:
@@ -328,6 +329,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (half == 0) { total = l + x[r]; x[r] = total; }
             ok = ok && pair_sync();
             if (half == 1) total = x[r];
+            if (p.sink_log2 != nullptr) total += exp2f(p.sink_log2[kvh * G + g] - m_ref);
             const float inv = 1.0f / total;
             __nv_bfloat16* dst = p.out + ((size_t)(row0_seq + tok0 + (row_valid ? t : 0)) * p.n_heads + kvh * G + g) * D;
 #pragma unroll
@@ -409,11 +411,11 @@ int mdma_attention_tc_supported(int n_heads, int n_kv_heads, int head_dim, int p
 }
 
 // q: rows of the fused projection [tokens_cap, row_width], queries first; caches [pages, page_size, kv_heads, head_dim].
-int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k_cache, const void* v_cache,
+static int attention_tc_run(const void* q, int q_stride, int q_rows_cap, const void* k_cache, const void* v_cache,
                       int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_slot,
                       const int* page_table, int max_pages, int page_size, void* out, int n_tokens, int n_seqs,
                       int max_new, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                      int* status, cudaStream_t stream) {
+                      int* status, const float* sink_log2, cudaStream_t stream) {
     MDMA_REQUIRE(mdma_attention_tc_supported(n_heads, n_kv_heads, head_dim, page_size),
                  "attention_tc: heads %d / kv heads %d / head_dim %d / page %d is outside its limits", n_heads, n_kv_heads, head_dim, page_size);
     MDMA_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_tc: query rows must be 16-byte aligned");
@@ -426,7 +428,7 @@ int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k
     p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
     p.out = (__nv_bfloat16*)out; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.group = G; p.tile_tokens = kTcRows / G; p.window = window; p.n_tokens = n_tokens;
-    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.sink_log2 = sink_log2;
     CUtensorMap mq, mk, mv;
     {   // queries: [tokens][heads][head_dim] inside rows of q_stride elements; box = 64 x G x tile_tokens
         const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)n_heads, (uint64_t)n_tokens, 1};
@@ -452,6 +454,27 @@ int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k
     cudaError_t e = launch_chained(attention_tc_kernel, grid, dim3(kTcThreadsA), kAttnTcSmem, stream, mq, mk, mv, p);
     if (e != cudaSuccess) return fail("attention_tc: launch failed: %s", cudaGetErrorString(e));
     return 0;
+}
+
+int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k_cache, const void* v_cache,
+                      int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_slot,
+                      const int* page_table, int max_pages, int page_size, void* out, int n_tokens, int n_seqs,
+                      int max_new, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                      int* status, cudaStream_t stream) {
+    return attention_tc_run(q, q_stride, q_rows_cap, k_cache, v_cache, n_pages, seq_start, seq_pos0, seq_slot, page_table,
+                            max_pages, page_size, out, n_tokens, n_seqs, max_new, n_heads, n_kv_heads, head_dim, window,
+                            scale, status, nullptr, stream);
+}
+
+// The same with a sink in every softmax (see AttnTcParams::sink_log2).
+int mdma_attention_tc_sink(const void* q, int q_stride, int q_rows_cap, const void* k_cache, const void* v_cache,
+                           int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_slot,
+                           const int* page_table, int max_pages, int page_size, void* out, int n_tokens, int n_seqs,
+                           int max_new, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                           int* status, const float* sink_log2, cudaStream_t stream) {
+    return attention_tc_run(q, q_stride, q_rows_cap, k_cache, v_cache, n_pages, seq_start, seq_pos0, seq_slot, page_table,
+                            max_pages, page_size, out, n_tokens, n_seqs, max_new, n_heads, n_kv_heads, head_dim, window,
+                            scale, status, sink_log2, stream);
 }
 
 }  // extern "C"

@@ -33,7 +33,8 @@ struct Ending {
     const void* bias;     // [n_features] or null
     const void* bias2;    // the second matrix's, or null
     int bias_dtype;       // DType of both
-    int act;              // Activation, gated products only
+    int act;              // Activation of a gated product's gate, or of a stored product when `store_act` is set
+    int store_act;        // a product that is stored: out = act(sum + bias) (a feed-forward without a gate)
 };
 __device__ __forceinline__ float ending_bias(const void* b, int dtype, int f) {
     if (b == nullptr) return 0.f;

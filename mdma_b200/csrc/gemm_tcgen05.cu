@@ -253,6 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int t = t0 + c + j;
                         float r = v[j] + b1;
                         if (MODE == kTcSwiGLU) r = gate_activation_fast(r, p.ending.act) * (u[j] + b2);
+                        if (MODE == kTcStore && p.ending.store_act) r = gate_activation_fast(r, p.ending.act);
                         if (MODE == kTcPartial) {
                             p.partial[((size_t)blockIdx.z * p.n_tokens + t) * p.n_features + f] = r;
                         } else if (p.out_f32) {
@@ -529,6 +530,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                             const int t = t0 + c + q;
                             float r = v[q] + b1;
                             if (MODE == kTcSwiGLU) r = gate_activation_fast(r, p.ending.act) * (u[q] + b2);
+                            if (MODE == kTcStore && p.ending.store_act) r = gate_activation_fast(r, p.ending.act);
                             if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
                             else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
                         }
@@ -567,7 +569,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 // out (=, +=) sum over splits of partial, in split order.
 template <int MODE>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int n_tokens, int n_features,
-                                     void* __restrict__ out, int ldo, int out_f32) {
+                                     void* __restrict__ out, int ldo, int out_f32, int store_act, int act) {
     chain_release();
     chain_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -575,6 +577,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     if (i >= total) return;
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * total + i];
+    if (MODE == kTcStore && store_act) acc = gate_activation_fast(acc, act);      // the sums are complete only here
     const size_t t = i / n_features, f = i % n_features;
     if (MODE == kTcAccumulate) reinterpret_cast<float*>(out)[t * ldo + f] += acc;
     else if (out_f32) reinterpret_cast<float*>(out)[t * ldo + f] = acc;
@@ -877,19 +880,24 @@ int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_coun
 
 // Sums the partial results of a K split into `out` (mode store) or adds them to it (mode accumulate),
 // in split order.
-int mdma_splitk_reduce(int mode, const float* partial, int splits, int n_tokens, int n_features, void* out,
-                       int ldo, int out_f32, cudaStream_t stream) {
+static int splitk_reduce_run(int mode, const float* partial, int splits, int n_tokens, int n_features, void* out,
+                             int ldo, int out_f32, int store_act, int act, cudaStream_t stream) {
     MDMA_REQUIRE(splits >= 1 && partial && out, "splitk_reduce: nothing to reduce");
     MDMA_REQUIRE(mode == kTcStore || mode == kTcAccumulate, "splitk_reduce: unknown mode %d", mode);
     const size_t total = (size_t)n_tokens * n_features;
     if (total == 0) return 0;
     const int blocks = (int)((total + 255) / 256);
     if (mode == kTcAccumulate)
-        launch_chained(splitk_reduce_kernel<kTcAccumulate>, dim3(blocks), dim3(256), 0, stream, partial, splits, n_tokens, n_features, out, ldo, out_f32);
+        launch_chained(splitk_reduce_kernel<kTcAccumulate>, dim3(blocks), dim3(256), 0, stream, partial, splits, n_tokens, n_features, out, ldo, out_f32, 0, 0);
     else
-        launch_chained(splitk_reduce_kernel<kTcStore>, dim3(blocks), dim3(256), 0, stream, partial, splits, n_tokens, n_features, out, ldo, out_f32);
+        launch_chained(splitk_reduce_kernel<kTcStore>, dim3(blocks), dim3(256), 0, stream, partial, splits, n_tokens, n_features, out, ldo, out_f32, store_act, act);
     MDMA_LAUNCH_OK("splitk_reduce");
     return 0;
+}
+
+int mdma_splitk_reduce(int mode, const float* partial, int splits, int n_tokens, int n_features, void* out,
+                       int ldo, int out_f32, cudaStream_t stream) {
+    return splitk_reduce_run(mode, partial, splits, n_tokens, n_features, out, ldo, out_f32, 0, 0, stream);
 }
 
 // `defer_reduce`: with a K split, leave the partial sums [splits, n_tokens, n_features] in `scratch`
@@ -899,6 +907,10 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
                  long scratch_floats, int* status, int defer_reduce, int* splits_used, int* sk_flags,
                  const void* bias, const void* bias2, int bias_dtype, int act, cudaStream_t stream) {
     if (splits_used) *splits_used = 1;
+    // bit 8 of `act`: the product is stored with the activation applied, out = act(a W^T + b)
+    const int store_act = (act >> 8) & 1;
+    act &= 0xff;
+    MDMA_REQUIRE(!store_act || (mode == kTcStore && !defer_reduce), "gemm_tc: an activation on the way out goes with a stored, complete product");
     MDMA_REQUIRE(n_tokens >= 0 && n_features > 0 && K > 0, "gemm_tc: bad sizes");
     MDMA_REQUIRE(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
     MDMA_REQUIRE(ldx % 8 == 0 && ldx >= K, "gemm_tc: activation pitch %d must be a multiple of 8 and at least K", ldx);
@@ -907,7 +919,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE(mode != kTcSwiGLU || w2, "gemm_tc: SwiGLU needs two weights");
     MDMA_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tc: unknown activation %d", act);
     MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_tc: unknown bias dtype %d", bias_dtype);
-    const Ending ending{bias, mode == kTcSwiGLU ? bias2 : nullptr, bias_dtype, act};
+    const Ending ending{bias, mode == kTcSwiGLU ? bias2 : nullptr, bias_dtype, act, store_act};
     MDMA_REQUIRE(mode != kTcAccumulate || out_f32, "gemm_tc: the residual stream is float");
     MDMA_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: unknown mode %d", mode);
     MDMA_REQUIRE(bn == 512 || (n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
@@ -962,7 +974,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     if (int rc = run_tc_bn<kTcPartial>(bn, x, ldx, w, w2, K, p, splits, stream)) return rc;
     if (splits_used) *splits_used = splits;
     if (defer_reduce) return 0;
-    return mdma_splitk_reduce(mode, scratch, splits, n_tokens, n_features, out, ldo, out_f32, stream);
+    return splitk_reduce_run(mode, scratch, splits, n_tokens, n_features, out, ldo, out_f32, store_act, act, stream);
 }
 
 }  // extern "C"

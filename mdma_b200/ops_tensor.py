@@ -175,11 +175,15 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
          w2: Optional[torch.Tensor] = None, m: Optional[int] = None,
          bn: Optional[int] = None, splits: Optional[int] = None, defer: bool = False,
          st: Optional[TensorState] = None, bias: Optional[torch.Tensor] = None,
-         bias2: Optional[torch.Tensor] = None, act: int = ops.ACT_SILU) -> None:
+         bias2: Optional[torch.Tensor] = None, act: int = ops.ACT_SILU, store_act: bool = False) -> None:
     """out[:m] (=, +=) a[:m] @ w.T (+ bias) on the tensor cores; the gated mode takes gate=w, up=w2 and
     gives act(gate) * up.
     `defer`: if the product is split over K, leave its partial sums for the next kernel
-    (a norm or the rotary write) to add up; see `take_pending`.  `st`: the engine's state."""
+    (a norm or the rotary write) to add up; see `take_pending`.  `st`: the engine's state.
+    `store_act` (stored products only): out = act(a @ w.T + bias), applied where the sums are complete."""
+    if store_act:
+        assert mode == ops.GEMM_STORE and not defer
+        act = act | 0x100
     _need_cuda(a, w, out, w2)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("the tensor-core product takes bfloat16 operands")
@@ -255,11 +259,15 @@ def attention_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int, page_si
 
 def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
               window: int, scale: float, splits: Optional[int] = None, impl: Optional[str] = None,
-              st: Optional[TensorState] = None) -> None:
+              st: Optional[TensorState] = None, sink_log2: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache (bfloat16).
     Steps that bring many tokens per sequence run on the tcgen05 kernel, single tokens on the
     decode kernel, what is between (or outside the tcgen05 kernel's limits) on the mma.sync kernel;
-    `impl` ("tc" or "mma") forces one."""
+    `impl` ("tc" or "mma") forces one.  `sink_log2` [n_heads] floats: a softmax with a sink, the learned
+    numbers times log2(e); each joins its head's denominators once, with no key and no value."""
+    if sink_log2 is not None:
+        _need_cuda(sink_log2)
+        assert sink_log2.dtype == torch.float32 and sink_log2.is_contiguous() and sink_log2.numel() == n_heads
     group = n_heads // n_kv_heads
     if impl is None and FORCED_ATTENTION:
         impl = FORCED_ATTENTION
@@ -274,11 +282,15 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
         assert view.k.is_contiguous() and view.v.is_contiguous()
         st = st or _device_state(qkv.device)
         flush_pending(qkv.device, st)
-        _call("tensor", "mdma_attention_tc", _ptr(qkv), _i(qkv.stride(0)), _i(qkv.shape[0]), _ptr(view.k),
-              _ptr(view.v), _i(view.k.shape[0]), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot),
-              _ptr(view.page_table), _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens),
-              _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale),
-              _ptr(st.status), _stream())
+        args = (_ptr(qkv), _i(qkv.stride(0)), _i(qkv.shape[0]), _ptr(view.k),
+                _ptr(view.v), _i(view.k.shape[0]), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot),
+                _ptr(view.page_table), _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens),
+                _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale),
+                _ptr(st.status))
+        if sink_log2 is None:
+            _call("tensor", "mdma_attention_tc", *args, _stream())
+        else:
+            _call("tensor", "mdma_attention_tc_sink", *args, _ptr(sink_log2), _stream())
         return
     _need_cuda(qkv, view.k, view.v, out, view.page_table)
     if qkv.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16:
@@ -290,12 +302,15 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
         splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st.sms,
                                   getattr(ctx, "most_seqs", None))
     st.need(ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0, "attention over split keys")
-    _call("tensor", "mdma_attention_mma_paged", _ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
-          _i(view.k.shape[0] if view.k.is_contiguous() and view.v.is_contiguous() else 0), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
-          _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs),
-          _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
-          _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status), _stream(),
-          launches=2 if splits > 1 else 1)
+    args = (_ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
+            _i(view.k.shape[0] if view.k.is_contiguous() and view.v.is_contiguous() else 0), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
+            _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs),
+            _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
+            _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status))
+    if sink_log2 is None:
+        _call("tensor", "mdma_attention_mma_paged", *args, _stream(), launches=2 if splits > 1 else 1)
+    else:
+        _call("tensor", "mdma_attention_mma_sink", *args, _ptr(sink_log2), _stream(), launches=2 if splits > 1 else 1)
 
 
 def fused_rotary_supported(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, rotary_dim: int) -> bool:

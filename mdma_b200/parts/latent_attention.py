@@ -62,6 +62,8 @@ class LatentAttention(Part):
         self.n_heads, self.dim, self.vdim, self.rank = int(p["heads"]), int(p["dim"]), int(p["vdim"]), int(p["kv_rank"])
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         self.window = int(p.get("window", 0) or 0)
+        # as the attention kernels and the engine's scratch plan see it: every head reads one shared head of the cache
+        self.n_kv_heads, self.head_dim = 1, self.rank
         self.q_width, self.v_width, self.lat_width = self.n_heads * self.dim, self.n_heads * self.vdim, self.n_heads * self.rank
 
     def check_limits(self, rt):
@@ -80,7 +82,8 @@ class LatentAttention(Part):
     def device_tensors(self):
         # the keys' map per head, transposed, so that it is applied to the queries as an ordinary product
         # (counted at four bytes an element: the plan is made before the compute dtype is known to the part)
-        return {"uk_t": ((self.n_heads, self.rank, self.dim), torch.float32)}
+        return {"uk_t": ((self.n_heads, self.rank, self.dim), torch.float32),
+                "sink_log2": ((self.n_heads,), torch.float32)}
 
     def kv_need(self):
         return KVNeed(1, self.rank, self.window, values=False)
@@ -110,6 +113,14 @@ class LatentAttention(Part):
         uk_t = rt.alloc(shape, uk.dtype) if rt.alloc is not None else torch.empty(shape, dtype=uk.dtype, device=uk.device)
         uk_t.copy_(uk.view(self.n_heads, self.dim, self.rank).transpose(1, 2))
         self.absorb = HeadwiseLinear(uk_t, rt)
+        # the tensor-core attention kernels work in powers of two: the sinks times log2(e), as floats
+        self.sink_log2 = (rt.alloc((self.n_heads,), torch.float32) if rt.alloc is not None
+                          else torch.empty(self.n_heads, dtype=torch.float32, device=uk.device))
+        self.sink_log2.copy_(self.sink.float() * 1.4426950408889634)
+        self._fast_ok = False
+        if rt.attention == "fast":
+            from .. import ops_tensor
+            self._fast_ok = ops_tensor.attention_supported(self.n_heads, 1, self.rank) and self.scale > 0
         self.expand = HeadwiseLinear(tensors["uv"].view(self.n_heads, self.vdim, self.rank), rt)
 
     def forward(self, ctx, h, x, view, owns_cache=True):
@@ -128,8 +139,18 @@ class LatentAttention(Part):
             ops.latent_norm_store(proj, self.q_width, self.latent_norm, self.eps, self.rank, ctx.tok_seq, ctx.tok_pos,
                                   ctx.seq_slot, view.page_table, view.max_pages, view.page_size, view.k, n)
         self.absorb.run(proj, q_lat, n)
-        ops.latent_attention(q_lat, view.k, self.sink, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, view.page_table,
-                             view.max_pages, view.page_size, o_lat, n, self.n_heads, self.rank, self.window, self.scale)
+        if self._fast_ok:
+            # the latent rows serve as the one key head and as the one value head
+            import dataclasses
+            from .. import ops_tensor
+            ops_tensor.attention(ctx, q_lat, dataclasses.replace(view, v=view.k), o_lat, self.n_heads, 1, self.rank,
+                                 self.window, self.scale, st=self.rt.tc, sink_log2=self.sink_log2)
+        else:
+            if self.rt.gemm == "tensor":
+                from .. import ops_tensor
+                ops_tensor.flush_pending(q_lat.device, self.rt.tc)
+            ops.latent_attention(q_lat, view.k, self.sink, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, view.page_table,
+                                 view.max_pages, view.page_size, o_lat, n, self.n_heads, self.rank, self.window, self.scale)
         self.expand.run(o_lat, v, n)
         if accumulate:
             self.o.accumulate(v, target, n, defer=False)

@@ -27,11 +27,12 @@ class Linear:
             from .. import ops_tensor
             self._tensor_ok = ops_tensor.gemm_supported(self.out_features, self.in_features)
 
-    def _run(self, mode: int, a: torch.Tensor, out: torch.Tensor, m: int, defer: bool = False) -> None:
+    def _run(self, mode: int, a: torch.Tensor, out: torch.Tensor, m: int, defer: bool = False,
+             store_act: bool = False) -> None:
         if self._tensor_ok:
             from .. import ops_tensor
             ops_tensor.gemm(a, self.w, out, mode, self.w2, m, defer=defer, st=self.rt.tc,
-                            bias=self.bias, bias2=self.bias2, act=self.act)
+                            bias=self.bias, bias2=self.bias2, act=self.act, store_act=store_act)
         else:
             if self.rt.gemm == "tensor":
                 from .. import ops_tensor
@@ -50,8 +51,7 @@ class Linear:
     def store_act(self, a, out, m):
         """out = act(a W^T + b): a feed-forward's first product when it has no gate."""
         if self._tensor_ok:
-            self._run(ops.GEMM_STORE, a, out, m)
-            ops.activation(out, m, self.act)
+            self._run(ops.GEMM_STORE, a, out, m, store_act=True)
         else:
             self._run(ops.GEMM_STORE_ACT, a, out, m)
 
