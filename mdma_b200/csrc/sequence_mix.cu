@@ -17,6 +17,13 @@
 
 namespace mdma {
 
+// Row-wise kernels run a grid of (rows, column parts): a step of a few rows still fills the device, and no
+// thread walks a row with one dependent load after another.
+static inline unsigned column_parts(int width) {
+    const int parts = (width + 255) / 256;
+    return (unsigned)(parts < 1 ? 1 : parts > 64 ? 64 : parts);
+}
+
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
@@ -33,7 +40,7 @@ dyt_norm_kernel(const float* __restrict__ x, const TW* __restrict__ w, const TW*
     const float a = to_float(alpha[0]);
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
     TO* yr = y + (size_t)r * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x)
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x)
         yr[e] = from_float<TO>(tanhf(a * xr[e]) * to_float(w[e]) + to_float(b[e]));
 }
 
@@ -55,7 +62,7 @@ dyt_shift_kernel(const float* __restrict__ x, const TW* __restrict__ w, const TW
     const float a = to_float(alpha[0]);
     const float* xr = x + (size_t)t * width;
     const float* prev = first ? state + (size_t)seq_slot[s] * state_stride : xr - width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) {
         const float we = to_float(w[e]), be = to_float(b[e]);
         const float cur = to_float(from_float<TO>(tanhf(a * xr[e]) * we + be));
         const float before = first ? prev[e] : to_float(from_float<TO>(tanhf(a * prev[e]) * we + be));
@@ -78,7 +85,7 @@ token_shift_kernel(const T* __restrict__ h, const TW* __restrict__ mu, const int
     const bool first = t == seq_start[s];
     const T* cur = h + (size_t)t * width;
     const float* kept = state + (size_t)seq_slot[s] * state_stride;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) {
         const float c = to_float(cur[e]);
         const float before = first ? kept[e] : to_float(cur[e - width]);
         hs[(size_t)t * width + e] = from_float<T>(c + (before - c) * to_float(mu[e]));
@@ -95,28 +102,40 @@ keep_last_rows_kernel(const T* __restrict__ rows, const int* __restrict__ seq_st
     const int s = blockIdx.x;
     const T* last = rows + (size_t)(seq_start[s + 1] - 1) * width;
     float* kept = state + (size_t)seq_slot[s] * state_stride;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) kept[e] = to_float(last[e]);
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) kept[e] = to_float(last[e]);
 }
 
 // ---------------------------------------------------------------- gated residual add
-// x[t,:] += sigmoid(g[t,:]) * y[t,:].  With `keep` the rows of `keep_rows` that end a sequence go to
-// the state as well (the token shift's kept row), which saves a launch.
+// x[t,:] += sigmoid(g[t,:]) * y[t,:].  With `keep_rows` the rows of it that end a sequence go to
+// the state as well (the token shift's kept row), which saves a launch.  With `splits` > 0, y is the sum of
+// that many partial results [split][row][width] (a K-split product whose reduction is done here).
 template <typename TG, typename TK>
 __global__ void __launch_bounds__(256)
-gated_add_kernel(float* __restrict__ x, const TG* __restrict__ g, const float* __restrict__ y, int width,
+gated_add_kernel(float* __restrict__ x, const TG* __restrict__ g, const float* __restrict__ y,
+                 const float* __restrict__ partial, int splits, size_t split_stride, int width,
                  const TK* __restrict__ keep_rows, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                  const int* __restrict__ seq_slot, float* __restrict__ state, long state_stride) {
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
     const size_t o = (size_t)t * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x)
-        x[o + e] = x[o + e] + sigmoid_f(to_float(g[o + e])) * y[o + e];
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x)
+    {
+        // y is either complete or still the K-split partial sums of the product that made it, added up here in split order
+        float v;
+        if (splits > 0) {
+            v = 0.f;
+            for (int sp = 0; sp < splits; ++sp) v += partial[(size_t)sp * split_stride + o + e];
+        } else {
+            v = y[o + e];
+        }
+        x[o + e] = x[o + e] + sigmoid_f(to_float(g[o + e])) * v;
+    }
     if (keep_rows != nullptr) {
         const int s = tok_seq[t];
         if (t == seq_start[s + 1] - 1) {
             float* kept = state + (size_t)seq_slot[s] * state_stride;
-            for (int e = threadIdx.x; e < width; e += blockDim.x) kept[e] = to_float(keep_rows[o + e]);
+            for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) kept[e] = to_float(keep_rows[o + e]);
         }
     }
 }
@@ -146,7 +165,7 @@ pack_pair_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) {
         out[(size_t)t * 2 * width + e] = from_float<T>(a[(size_t)t * width + e]);
         out[(size_t)t * 2 * width + width + e] = from_float<T>(b[(size_t)t * width + e]);
     }
@@ -181,6 +200,68 @@ mingru_scan_kernel(const float* __restrict__ p, int p_stride, const TW* __restri
     *kept = S;
 }
 
+// The same recurrence for steps that bring many rows per sequence: it is linear in S (S_t = a_t S_(t-1) + b_t with
+// a = 1 - z, b = z * candidate), so a sequence's rows are cut into kGruChunks runs; a thread walks one run of one
+// channel from zero and keeps the run's product of a and its last value, the runs' starting values follow from
+// those in order, and every run is walked again from its starting value, this time writing the outputs.  The
+// association of the products differs from the row-by-row kernel's, so results agree to rounding, not to the bit:
+// the serving engine uses this kernel, the 32-bit engine the one above.
+constexpr int kGruChunks = 32, kGruChannels = 32;
+
+template <typename TO, typename TW>
+__global__ void __launch_bounds__(kGruChunks * kGruChannels)
+mingru_scan_chunked_kernel(const float* __restrict__ p, int p_stride, const TW* __restrict__ bz, const TW* __restrict__ bu,
+                           const int* __restrict__ seq_start, const int* __restrict__ seq_slot, float* __restrict__ state,
+                           long state_stride, TO* __restrict__ out, int width) {
+    chain_release();
+    chain_wait();
+    __shared__ float sA[kGruChunks][kGruChannels], sB[kGruChunks][kGruChannels];
+    const int lane_c = threadIdx.x % kGruChannels, k = threadIdx.x / kGruChannels;
+    const int c = blockIdx.x * kGruChannels + lane_c;
+    const int s = blockIdx.y;
+    const bool live = c < width;
+    const int t0 = seq_start[s], t1 = seq_start[s + 1];
+    const int run = (t1 - t0 + kGruChunks - 1) / kGruChunks;
+    const int lo = min(t1, t0 + k * run), hi = min(t1, lo + run);
+    const float zb = live ? to_float(bz[c]) : 0.f, ub = live ? to_float(bu[c]) : 0.f;
+    float A = 1.f, B = 0.f;
+    if (live) {
+        for (int t = lo; t < hi; ++t) {
+            const float* row = p + (size_t)t * p_stride;
+            const float z = sigmoid_f(row[c] + zb);
+            const float u = row[width + c] + ub;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+            A *= 1.0f - z;
+            B = (1.0f - z) * B + z * cand;
+        }
+    }
+    sA[k][lane_c] = A;
+    sB[k][lane_c] = B;
+    __syncthreads();
+    if (k == 0 && live) {
+        float* kept = state + (size_t)seq_slot[s] * state_stride + c;
+        float S = *kept;
+        for (int j = 0; j < kGruChunks; ++j) {
+            const float next = sA[j][lane_c] * S + sB[j][lane_c];
+            sB[j][lane_c] = S;                       // the run's starting value
+            S = next;
+        }
+        *kept = S;
+    }
+    __syncthreads();
+    if (live) {
+        float S = sB[k][lane_c];
+        for (int t = lo; t < hi; ++t) {
+            const float* row = p + (size_t)t * p_stride;
+            const float z = sigmoid_f(row[c] + zb);
+            const float u = row[width + c] + ub;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+            S = (1.0f - z) * S + z * cand;
+            out[(size_t)t * width + c] = from_float<TO>(S * silu_f(row[2 * width + c]));
+        }
+    }
+}
+
 // ---------------------------------------------------------------- short causal convolution
 // out[t,c] = silu(sum_j w[c,j] * in(t - (taps-1) + j, c) + b[c]); in(.) is column in_col + c of the
 // projection rows of this step, or, before the step's first row of the sequence, the kept inputs
@@ -197,7 +278,7 @@ causal_conv_silu_kernel(const float* __restrict__ proj, int proj_stride, int in_
     const int s = tok_seq[t];
     const int t0 = seq_start[s];
     const float* kept = state + (size_t)seq_slot[s] * state_stride;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float acc = to_float(b[c]);
         for (int j = 0; j < taps; ++j) {
             const int src = t - (taps - 1) + j;            // a row of this step, or before it
@@ -240,15 +321,25 @@ conv_keep_kernel(const float* __restrict__ proj, int proj_stride, int in_col, in
 // `conv` rows hold [x: heads*vdim | B: groups*N | C: groups*N] after the convolution, `proj` rows the
 // raw dt at column dt_col + h.  A block owns VB value columns of one (sequence, head); NP lanes share a
 // column, each with NPER of the N state rows in registers; the step's rows are staged through shared
-// memory sixteen at a time.  The state of a (sequence, head, column) is read and written by the same threads.
+// memory sixteen at a time.  The state of a (sequence, head, column) is read and written by the same threads;
+// it is kept as [head][column][N], so that the lanes that share a column touch neighbouring words.
+//
+// Steps that bring many rows per sequence cut every sequence into runs of `chunk_rows` rows that are walked side
+// by side (the recurrence is linear in S): pass kScanLocal walks each run but the last from S = 0 and leaves the
+// run's last S and its total decay exp(-exp(A_log) sum dt) in scratch; mamba2_chunk_starts_kernel turns those, in
+// order, into every run's starting S; pass kScanFrom walks every run from its starting S and writes y (the last run
+// writes the sequence's state).  Twice the arithmetic for as many times the blocks; equal to the one-pass walk up
+// to rounding, so the serving engine uses it and the 32-bit engine does not.
 constexpr int kScanRows = 16;
+enum ScanPass : int { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 
-template <int NPER, typename TW>
+template <int NPER, typename TW, int PASS>
 __global__ void __launch_bounds__(128)
 mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float* __restrict__ proj, int proj_stride,
                    int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log, const TW* __restrict__ D,
                    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, float* __restrict__ state,
-                   long state_stride, float* __restrict__ y, int heads, int vdim, int N, int G, int NP) {
+                   long state_stride, float* __restrict__ y, int heads, int vdim, int N, int G, int NP,
+                   int chunk_rows, int max_chunks, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
     chain_release();
     chain_wait();
     extern __shared__ float sm[];
@@ -259,21 +350,35 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
     float* sx = sC + kScanRows * Npad;
     float* sdt = sx + kScanRows * VB;
     float* sa = sdt + kScanRows;
-    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VB;
+    const int s = PASS == kScanWhole ? blockIdx.x : blockIdx.x / max_chunks;
+    const int run = PASS == kScanWhole ? 0 : blockIdx.x % max_chunks;
+    const int h = blockIdx.y, v0 = blockIdx.z * VB;
+    int t_begin = seq_start[s], t_end = seq_start[s + 1];
+    bool last_run = true;
+    if (PASS != kScanWhole) {
+        const int runs = (t_end - t_begin + chunk_rows - 1) / chunk_rows;
+        last_run = run == runs - 1;
+        if (run >= runs || (PASS == kScanLocal && last_run)) return;       // the whole block leaves together
+        t_begin += run * chunk_rows;
+        t_end = min(t_end, t_begin + chunk_rows);
+    }
+    const size_t state_floats = (size_t)heads * N * vdim;
     const int g = h / (heads / G);
     const int np = threadIdx.x % NP, vl = threadIdx.x / NP;
     const int v = v0 + vl;
     const bool vok = v < vdim;
     const int inner = heads * vdim;
     float* Sg = state + (size_t)seq_slot[s] * state_stride + (size_t)h * N * vdim;
+    float* Sc = PASS == kScanWhole ? nullptr : chunk_state + (size_t)blockIdx.x * state_floats + (size_t)h * N * vdim;
+    const float* Sfrom = PASS == kScanWhole ? Sg : Sc;
     float S[NPER];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
         const int n = np * NPER + i;
-        S[i] = (vok && n < N) ? Sg[(size_t)n * vdim + v] : 0.f;
+        S[i] = (PASS != kScanLocal && vok && n < N) ? Sfrom[(size_t)v * N + n] : 0.f;
     }
+    float dt_sum = 0.f;
     const float rate = expf(to_float(A_log[h])), Dh = to_float(D[h]), bias = to_float(dt_bias[h]);
-    const int t_begin = seq_start[s], t_end = seq_start[s + 1];
     for (int t0 = t_begin; t0 < t_end; t0 += kScanRows) {
         const int nt = min(kScanRows, t_end - t0);
         __syncthreads();
@@ -281,7 +386,7 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
             const int tt = i / Npad, n = i % Npad;
             const float* row = conv + (size_t)(t0 + tt) * conv_stride + inner + g * N;
             sB[i] = n < N ? row[n] : 0.f;
-            sC[i] = n < N ? row[G * N + n] : 0.f;
+            if (PASS != kScanLocal) sC[i] = n < N ? row[G * N + n] : 0.f;
         }
         for (int i = threadIdx.x; i < nt * VB; i += blockDim.x) {
             const int tt = i / VB, vv = i % VB;
@@ -293,6 +398,8 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
             sa[i] = expf(-rate * d);
         }
         __syncthreads();
+        if (PASS == kScanLocal && threadIdx.x == 0)
+            for (int tt = 0; tt < nt; ++tt) dt_sum += sdt[tt];
         for (int tt = 0; tt < nt; ++tt) {
             const float a = sa[tt], xv = sx[tt * VB + vl], dtx = sdt[tt] * xv;
             const float* Bt = sB + tt * Npad + np * NPER;
@@ -301,24 +408,55 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
 #pragma unroll
             for (int i = 0; i < NPER; ++i) {
                 S[i] = fmaf(a, S[i], dtx * Bt[i]);
-                acc = fmaf(S[i], Ct[i], acc);
+                if (PASS != kScanLocal) acc = fmaf(S[i], Ct[i], acc);
             }
-            for (int o = NP >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (np == 0 && vok) y[(size_t)(t0 + tt) * inner + h * vdim + v] = acc + Dh * xv;
+            if (PASS != kScanLocal) {
+                for (int o = NP >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (np == 0 && vok) y[(size_t)(t0 + tt) * inner + h * vdim + v] = acc + Dh * xv;
+            }
         }
     }
+    float* Sto = PASS == kScanLocal ? Sc : (last_run ? Sg : nullptr);
+    if (Sto != nullptr) {
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-        const int n = np * NPER + i;
-        if (vok && n < N) Sg[(size_t)n * vdim + v] = S[i];
+        for (int i = 0; i < NPER; ++i) {
+            const int n = np * NPER + i;
+            if (vok && n < N) Sto[(size_t)v * N + n] = S[i];
+        }
+    }
+    if (PASS == kScanLocal && threadIdx.x == 0 && blockIdx.z == 0)
+        chunk_decay[(size_t)blockIdx.x * heads + h] = expf(-rate * dt_sum);
+}
+
+// The runs' starting states, in order: start[0] = the sequence's state, start[r+1] = decay[r] * start[r] + local[r].
+// `chunk_state` holds local[r] on entry and start[r] on return.  One thread per state element.
+__global__ void __launch_bounds__(256)
+mamba2_chunk_starts_kernel(const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                           const float* __restrict__ state, long state_stride, float* __restrict__ chunk_state,
+                           const float* __restrict__ chunk_decay, int heads, int per_head, int chunk_rows, int max_chunks) {
+    chain_release();
+    chain_wait();
+    const size_t state_floats = (size_t)heads * per_head;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = blockIdx.y;
+    if (e >= state_floats) return;
+    const int h = (int)(e / per_head);
+    const int runs = (seq_start[s + 1] - seq_start[s] + chunk_rows - 1) / chunk_rows;
+    float cur = state[(size_t)seq_slot[s] * state_stride + e];
+    for (int r = 0; r < runs; ++r) {
+        const size_t at = (size_t)s * max_chunks + r;
+        const float local = r < runs - 1 ? chunk_state[at * state_floats + e] : 0.f;
+        chunk_state[at * state_floats + e] = cur;
+        if (r < runs - 1) cur = chunk_decay[at * heads + h] * cur + local;
     }
 }
 
 // ---------------------------------------------------------------- gate, then norm in groups
 // v = y * silu(z); each of `groups` equal parts of the row is divided by its own root mean square
 // (eps inside the root) and multiplied by w.  One block per (row, part).
-template <typename TO, typename TW>
-__global__ void __launch_bounds__(256)
+// PER > 0: each thread keeps PER gated values of the part in registers (one read of y and z).
+template <typename TO, typename TW, int PER>
+__global__ void __launch_bounds__(1024)
 gated_group_rmsnorm_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ z, int z_stride,
                            const TW* __restrict__ w, TO* __restrict__ out, int width, int groups, float eps) {
     chain_release();
@@ -329,6 +467,23 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, int y_stride, const floa
     const float* yr = y + (size_t)t * y_stride + base;
     const float* zr = z + (size_t)t * z_stride + base;
     float ss = 0.f;
+    if (PER > 0) {
+        float v[PER > 0 ? PER : 1];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            v[i] = e < size ? yr[e] * silu_f(zr[e]) : 0.f;
+            ss += v[i] * v[i];
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)size + eps);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < size) out[(size_t)t * width + base + e] = from_float<TO>(v[i] * scale * to_float(w[base + e]));
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < size; e += blockDim.x) {
         const float v = yr[e] * silu_f(zr[e]);
         ss += v * v;
@@ -355,7 +510,7 @@ int mdma_dyt_norm(const float* x, const void* w, const void* b, const void* alph
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "dyt_norm: bad sizes");
     if (n_rows == 0) return 0;
     MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
-        launch_chained(dyt_norm_kernel<TO, TW>, dim3(n_rows), dim3(256), 0, stream, x, (const TW*)w, (const TW*)b,
+        launch_chained(dyt_norm_kernel<TO, TW>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TW*)w, (const TW*)b,
                        (const TW*)alpha, rows, (TO*)y, width));
     MDMA_LAUNCH_OK("dyt_norm");
     return 0;
@@ -367,7 +522,7 @@ int mdma_dyt_shift(const float* x, const void* w, const void* b, const void* alp
     MDMA_REQUIRE(n_rows >= 0 && width > 0 && state_stride >= width, "dyt_shift: bad sizes");
     if (n_rows == 0) return 0;
     MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
-        launch_chained(dyt_shift_kernel<TO, TW>, dim3(n_rows), dim3(256), 0, stream, x, (const TW*)w, (const TW*)b,
+        launch_chained(dyt_shift_kernel<TO, TW>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TW*)w, (const TW*)b,
                        (const TW*)alpha, (const TW*)mu, tok_seq, seq_start, seq_slot, state, state_stride,
                        (TO*)h, (TO*)hs, width));
     MDMA_LAUNCH_OK("dyt_shift");
@@ -380,7 +535,7 @@ int mdma_token_shift(const void* h, int dtype, const void* mu, int mu_dtype, con
     MDMA_REQUIRE(n_rows >= 0 && width > 0 && state_stride >= width, "token_shift: bad sizes");
     if (n_rows == 0) return 0;
     MDMA_DISPATCH_2(dtype, T, mu_dtype, TW,
-        launch_chained(token_shift_kernel<T, TW>, dim3(n_rows), dim3(256), 0, stream, (const T*)h, (const TW*)mu,
+        launch_chained(token_shift_kernel<T, TW>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, (const T*)h, (const TW*)mu,
                        tok_seq, seq_start, seq_slot, state, state_stride, (T*)hs, width));
     MDMA_LAUNCH_OK("token_shift");
     return 0;
@@ -391,21 +546,22 @@ int mdma_keep_last_rows(const void* rows, int dtype, const int* seq_start, const
     MDMA_REQUIRE(n_seqs >= 0 && width > 0 && state_stride >= width, "keep_last_rows: bad sizes");
     if (n_seqs == 0) return 0;
     MDMA_DISPATCH_DTYPE(dtype, T,
-        launch_chained(keep_last_rows_kernel<T>, dim3(n_seqs), dim3(256), 0, stream, (const T*)rows, seq_start,
+        launch_chained(keep_last_rows_kernel<T>, dim3(n_seqs, column_parts(width)), dim3(256), 0, stream, (const T*)rows, seq_start,
                        seq_slot, state, state_stride, width));
     MDMA_LAUNCH_OK("keep_last_rows");
     return 0;
 }
 
-int mdma_gated_add(float* x, const void* g, int g_dtype, const float* y, int n_rows, int width, const void* keep_rows,
+int mdma_gated_add(float* x, const void* g, int g_dtype, const float* y, const float* partial, int splits,
+                   long split_stride, int n_rows, int width, const void* keep_rows,
                    int keep_dtype, const int* tok_seq, const int* seq_start, const int* seq_slot, float* state,
                    long state_stride, cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "gated_add: bad sizes");
     MDMA_REQUIRE(keep_rows == nullptr || (state != nullptr && state_stride >= width), "gated_add: no place for the kept rows");
     if (n_rows == 0) return 0;
     MDMA_DISPATCH_2(g_dtype, TG, keep_dtype, TK,
-        launch_chained(gated_add_kernel<TG, TK>, dim3(n_rows), dim3(256), 0, stream, x, (const TG*)g, y, width,
-                       (const TK*)keep_rows, tok_seq, seq_start, seq_slot, state, state_stride));
+        launch_chained(gated_add_kernel<TG, TK>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TG*)g, y, partial,
+                       partial ? splits : 0, (size_t)split_stride, width, (const TK*)keep_rows, tok_seq, seq_start, seq_slot, state, state_stride));
     MDMA_LAUNCH_OK("gated_add");
     return 0;
 }
@@ -431,17 +587,25 @@ int mdma_softcap(float* v, long n, float cap, cudaStream_t stream) {
 int mdma_pack_pair(const float* a, const float* b, void* out, int dtype, int n_rows, int width, cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "pack_pair: bad sizes");
     if (n_rows == 0) return 0;
-    MDMA_DISPATCH_DTYPE(dtype, T, launch_chained(pack_pair_kernel<T>, dim3(n_rows), dim3(256), 0, stream, a, b, (T*)out, width));
+    MDMA_DISPATCH_DTYPE(dtype, T, launch_chained(pack_pair_kernel<T>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, a, b, (T*)out, width));
     MDMA_LAUNCH_OK("pack_pair");
     return 0;
 }
 
 int mdma_mingru_scan(const float* p, int p_stride, const void* bz, const void* bu, int b_dtype, const int* seq_start,
                      const int* seq_slot, float* state, long state_stride, void* out, int out_dtype, int n_seqs,
-                     int width, cudaStream_t stream) {
+                     int width, int chunked, cudaStream_t stream) {
     MDMA_REQUIRE(n_seqs >= 0 && width > 0 && p_stride >= 3 * width && state_stride >= width, "mingru_scan: bad sizes");
     MDMA_REQUIRE(n_seqs <= 65535, "mingru_scan: too many sequences (%d)", n_seqs);
     if (n_seqs == 0) return 0;
+    if (chunked) {
+        MDMA_DISPATCH_2(out_dtype, TO, b_dtype, TW,
+            launch_chained(mingru_scan_chunked_kernel<TO, TW>, dim3((width + kGruChannels - 1) / kGruChannels, n_seqs),
+                           dim3(kGruChunks * kGruChannels), 0, stream, p, p_stride, (const TW*)bz, (const TW*)bu, seq_start,
+                           seq_slot, state, state_stride, (TO*)out, width));
+        MDMA_LAUNCH_OK("mingru_scan_chunked");
+        return 0;
+    }
     MDMA_DISPATCH_2(out_dtype, TO, b_dtype, TW,
         launch_chained(mingru_scan_kernel<TO, TW>, dim3((width + 127) / 128, n_seqs), dim3(128), 0, stream, p, p_stride,
                        (const TW*)bz, (const TW*)bu, seq_start, seq_slot, state, state_stride, (TO*)out, width));
@@ -459,7 +623,7 @@ int mdma_causal_conv_silu(const float* proj, int proj_stride, int in_col, const 
     MDMA_REQUIRE(n_seqs <= 65535, "causal_conv: too many sequences (%d)", n_seqs);
     if (n_rows == 0) return 0;
     MDMA_DISPATCH_2(w_dtype, TW, b_dtype, TB,
-        launch_chained(causal_conv_silu_kernel<TW, TB>, dim3(n_rows), dim3(256), 0, stream, proj, proj_stride, in_col,
+        launch_chained(causal_conv_silu_kernel<TW, TB>, dim3(n_rows, column_parts(channels)), dim3(256), 0, stream, proj, proj_stride, in_col,
                        (const TW*)w, (const TB*)b, taps, channels, tok_seq, seq_start, seq_slot, (const float*)state,
                        state_stride, out));
     MDMA_LAUNCH_OK("causal_conv_silu");
@@ -471,10 +635,13 @@ int mdma_causal_conv_silu(const float* proj, int proj_stride, int in_col, const 
     return 0;
 }
 
+// `chunk_rows` > 0: every sequence is walked as runs of that many rows side by side (at most `max_chunks` runs a
+// sequence); `scratch` then holds n_seqs * max_chunks * (heads * N * vdim + heads) floats.
 int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int proj_stride, int dt_col,
                      const void* dt_bias, const void* A_log, const void* D, int w_dtype, const int* seq_start,
                      const int* seq_slot, float* state, long state_stride, float* y, int n_seqs, int heads, int vdim,
-                     int N, int G, cudaStream_t stream) {
+                     int N, int G, int chunk_rows, int max_chunks, float* scratch, long scratch_floats,
+                     cudaStream_t stream) {
     MDMA_REQUIRE(heads > 0 && vdim > 0 && N > 0 && G > 0 && heads % G == 0, "mamba2_scan: bad geometry");
     MDMA_REQUIRE(N <= 256, "mamba2_scan: state size %d is beyond the kernel's 256", N);
     MDMA_REQUIRE(state_stride >= (long)heads * N * vdim, "mamba2_scan: the state rows are too short");
@@ -487,10 +654,34 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     const size_t smem = sizeof(float) * (size_t)(2 * kScanRows * np * nper + kScanRows * vb + 2 * kScanRows);
     dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb);
     MDMA_REQUIRE(grid.z <= 65535, "mamba2_scan: value size %d is too large", vdim);
+    if (chunk_rows > 0) {
+        const long state_floats = (long)heads * N * vdim;
+        const long slots = (long)n_seqs * max_chunks;
+        MDMA_REQUIRE(max_chunks >= 1 && slots <= 65535 * 16l && scratch != nullptr && scratch_floats >= slots * (state_floats + heads),
+                     "mamba2_scan: %ld runs need %ld floats of scratch, %ld given", slots, slots * (state_floats + heads), scratch_floats);
+        float* chunk_state = scratch;
+        float* chunk_decay = scratch + slots * state_floats;
+        dim3 cgrid((unsigned)slots, heads, grid.z);
+        MDMA_DISPATCH_DTYPE(w_dtype, TW,
+            launch_chained(mamba2_scan_kernel<8, TW, kScanLocal>, cgrid, dim3(128), smem, stream, conv, conv_stride, proj,
+                           proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,
+                           state, state_stride, y, heads, vdim, N, G, np, chunk_rows, max_chunks, chunk_state, chunk_decay));
+        MDMA_LAUNCH_OK("mamba2_scan (runs from zero)");
+        launch_chained(mamba2_chunk_starts_kernel, dim3((unsigned)((state_floats + 255) / 256), n_seqs), dim3(256), 0, stream,
+                       seq_start, seq_slot, (const float*)state, state_stride, chunk_state, (const float*)chunk_decay, heads,
+                       N * vdim, chunk_rows, max_chunks);
+        MDMA_LAUNCH_OK("mamba2_chunk_starts");
+        MDMA_DISPATCH_DTYPE(w_dtype, TW,
+            launch_chained(mamba2_scan_kernel<8, TW, kScanFrom>, cgrid, dim3(128), smem, stream, conv, conv_stride, proj,
+                           proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,
+                           state, state_stride, y, heads, vdim, N, G, np, chunk_rows, max_chunks, chunk_state, chunk_decay));
+        MDMA_LAUNCH_OK("mamba2_scan (runs from their starts)");
+        return 0;
+    }
     MDMA_DISPATCH_DTYPE(w_dtype, TW,
-        launch_chained(mamba2_scan_kernel<8, TW>, grid, dim3(128), smem, stream, conv, conv_stride, proj, proj_stride,
+        launch_chained(mamba2_scan_kernel<8, TW, kScanWhole>, grid, dim3(128), smem, stream, conv, conv_stride, proj, proj_stride,
                        dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot, state,
-                       state_stride, y, heads, vdim, N, G, np));
+                       state_stride, y, heads, vdim, N, G, np, 0, 1, (float*)nullptr, (float*)nullptr));
     MDMA_LAUNCH_OK("mamba2_scan");
     return 0;
 }
@@ -500,9 +691,20 @@ int mdma_gated_group_rmsnorm(const float* y, int y_stride, const float* z, int z
     MDMA_REQUIRE(width > 0 && groups > 0 && width % groups == 0, "gated_group_rmsnorm: %d columns in %d parts", width, groups);
     MDMA_REQUIRE(groups <= 65535, "gated_group_rmsnorm: too many parts");
     if (n_rows == 0) return 0;
-    MDMA_DISPATCH_2(out_dtype, TO, w_dtype, TW,
-        launch_chained(gated_group_rmsnorm_kernel<TO, TW>, dim3(n_rows, groups), dim3(256), 0, stream, y, y_stride, z,
-                       z_stride, (const TW*)w, (TO*)out, width, groups, eps));
+    const int size = width / groups;
+    if (size <= 1024) {
+        MDMA_DISPATCH_2(out_dtype, TO, w_dtype, TW,
+            launch_chained(gated_group_rmsnorm_kernel<TO, TW, 4>, dim3(n_rows, groups), dim3(256), 0, stream, y, y_stride, z,
+                           z_stride, (const TW*)w, (TO*)out, width, groups, eps));
+    } else if (size <= 8192) {
+        MDMA_DISPATCH_2(out_dtype, TO, w_dtype, TW,
+            launch_chained(gated_group_rmsnorm_kernel<TO, TW, 8>, dim3(n_rows, groups), dim3(1024), 0, stream, y, y_stride, z,
+                           z_stride, (const TW*)w, (TO*)out, width, groups, eps));
+    } else {
+        MDMA_DISPATCH_2(out_dtype, TO, w_dtype, TW,
+            launch_chained(gated_group_rmsnorm_kernel<TO, TW, 0>, dim3(n_rows, groups), dim3(1024), 0, stream, y, y_stride, z,
+                           z_stride, (const TW*)w, (TO*)out, width, groups, eps));
+    }
     MDMA_LAUNCH_OK("gated_group_rmsnorm");
     return 0;
 }

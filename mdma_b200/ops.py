@@ -313,8 +313,10 @@ def keep_last_rows(rows, seq_start, seq_slot, state, n_seqs: int) -> None:
           sp, ss, _i(n_seqs), _i(rows.shape[1]), _stream())
 
 
-def gated_add(x, g, y, n_rows: int, keep_rows=None, tok_seq=None, seq_start=None, seq_slot=None, state=None) -> None:
-    """x += sigmoid(g) * y (x, y float).  With `keep_rows` each sequence's last row of it goes to `state`."""
+def gated_add(x, g, y, n_rows: int, keep_rows=None, tok_seq=None, seq_start=None, seq_slot=None, state=None,
+              partial=None, splits: int = 0, split_stride: int = 0) -> None:
+    """x += sigmoid(g) * y (x, y float).  With `keep_rows` each sequence's last row of it goes to `state`.
+    With `partial` [splits, rows, width] floats, y is their sum (a K-split product not yet added up)."""
     _need_cuda(x, g, y, keep_rows, tok_seq, seq_start, seq_slot, state)
     width = x.shape[1]
     assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and g.is_contiguous()
@@ -323,7 +325,8 @@ def gated_add(x, g, y, n_rows: int, keep_rows=None, tok_seq=None, seq_start=None
     if keep_rows is not None:
         assert keep_rows.is_contiguous() and keep_rows.shape[1] == width
         sp, ss = _state(state)
-    _call("core", "mdma_gated_add", _ptr(x), _ptr(g), _i(dtype_code(g.dtype)), _ptr(y), _i(n_rows), _i(width),
+    _call("core", "mdma_gated_add", _ptr(x), _ptr(g), _i(dtype_code(g.dtype)), _ptr(y), _ptr(partial),
+          _i(splits if partial is not None else 0), ctypes.c_long(split_stride), _i(n_rows), _i(width),
           _ptr(keep_rows), _i(dtype_code(keep_rows.dtype) if keep_rows is not None else F32), _ptr(tok_seq),
           _ptr(seq_start), _ptr(seq_slot), sp, ss, _stream())
 
@@ -351,14 +354,15 @@ def pack_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, n_rows: int) 
     _call("core", "mdma_pack_pair", _ptr(a), _ptr(b), _ptr(out), _i(dtype_code(out.dtype)), _i(n_rows), _i(width), _stream())
 
 
-def mingru_scan(p, bz, bu, seq_start, seq_slot, state, out, n_seqs: int, width: int) -> None:
+def mingru_scan(p, bz, bu, seq_start, seq_slot, state, out, n_seqs: int, width: int, chunked: bool = False) -> None:
     """p [T, 3*width] float = the three projections (z | u | g); runs S = (1-z) S + z cand over each
-    sequence's rows and writes S * silu(g)."""
+    sequence's rows and writes S * silu(g).  `chunked`: the kernel for steps of many rows per sequence, which
+    walks 32 runs of a sequence side by side (equal to the row-by-row kernel up to rounding)."""
     _need_cuda(p, bz, bu, seq_start, seq_slot, state, out)
     assert p.dtype == torch.float32 and p.stride(1) == 1 and p.shape[1] == 3 * width and out.is_contiguous() and out.shape[1] == width
     sp, ss = _state(state)
     _call("core", "mdma_mingru_scan", _ptr(p), _i(p.stride(0)), _ptr(bz), _ptr(bu), _i(_same_dtype(bz, bu)),
-          _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out), _i(dtype_code(out.dtype)), _i(n_seqs), _i(width), _stream())
+          _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out), _i(dtype_code(out.dtype)), _i(n_seqs), _i(width), _i(int(chunked)), _stream())
 
 
 def causal_conv_silu(proj, in_col: int, w, b, taps: int, channels: int, tok_seq, seq_start, seq_slot, state, out,
@@ -376,16 +380,22 @@ def causal_conv_silu(proj, in_col: int, w, b, taps: int, channels: int, tok_seq,
 
 
 def mamba2_scan(conv, proj, dt_col: int, dt_bias, a_log, d, seq_start, seq_slot, state, y, n_seqs: int, heads: int,
-                vdim: int, n_state: int, groups: int) -> None:
+                vdim: int, n_state: int, groups: int, chunk_rows: int = 0, max_chunks: int = 1, scratch=None) -> None:
     """The selective scan over each sequence's rows; `conv` rows are [x | B | C] after the convolution,
-    `proj` holds the raw step sizes at columns dt_col + head; state [slots, heads * n_state * vdim] float."""
+    `proj` holds the raw step sizes at columns dt_col + head; state [slots, heads * n_state * vdim] float.
+    `chunk_rows` > 0: sequences are walked as runs of that many rows side by side (`max_chunks`: the most runs
+    of a sequence; `scratch`: n_seqs * max_chunks * (state size + heads) floats); equal up to rounding."""
+    _need_cuda(scratch)
+    assert chunk_rows == 0 or (scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous())
     _need_cuda(conv, proj, dt_bias, a_log, d, seq_start, seq_slot, state, y)
     assert conv.dtype == proj.dtype == y.dtype == torch.float32 and conv.stride(1) == 1 and proj.stride(1) == 1
     assert y.is_contiguous() and y.shape[1] == heads * vdim and conv.shape[1] == heads * vdim + 2 * groups * n_state
     sp, ss = _state(state)
     _call("core", "mdma_mamba2_scan", _ptr(conv), _i(conv.stride(0)), _ptr(proj), _i(proj.stride(0)), _i(dt_col),
           _ptr(dt_bias), _ptr(a_log), _ptr(d), _i(_same_dtype(dt_bias, a_log, d)), _ptr(seq_start), _ptr(seq_slot),
-          sp, ss, _ptr(y), _i(n_seqs), _i(heads), _i(vdim), _i(n_state), _i(groups), _stream())
+          sp, ss, _ptr(y), _i(n_seqs), _i(heads), _i(vdim), _i(n_state), _i(groups), _i(chunk_rows), _i(max_chunks),
+          _ptr(scratch), ctypes.c_long(scratch.numel() if scratch is not None else 0), _stream(),
+          launches=3 if chunk_rows > 0 else 1)
 
 
 def gated_group_rmsnorm(y, z, w, out, n_rows: int, groups: int, eps: float) -> None:

@@ -120,7 +120,8 @@ class ShiftGatedBlock:
     @staticmethod
     def _run(ctx, part, h, y, *more):
         if hasattr(part, "produce"):
-            part.produce(ctx, h, y, *more)
+            # the gate's kernel adds up what a K-split product leaves (see ResidualGate.apply)
+            part.produce(ctx, h, y, *more, defer=True)
             return
         y[:ctx.n_tokens].zero_()
         part.forward(ctx, h, y, *more)

@@ -68,11 +68,21 @@ class ResidualGate(Part):
         self.proj.store(h, g, ctx.n_tokens)
 
     def apply(self, ctx, x, g, y, keep_rows=None, state=None):
-        """x += sigmoid(g) * y; with `keep_rows`, each sequence's last row of it goes to `state` in the same pass."""
+        """x += sigmoid(g) * y; with `keep_rows`, each sequence's last row of it goes to `state` in the same pass.
+        If the product that made y left K-split partial sums, they are added up here instead of in a launch of their own."""
+        partial, splits, stride = None, 0, 0
+        if self.rt.gemm == "tensor":
+            from .. import ops_tensor
+            pend = ops_tensor.take_pending(y, ops.GEMM_STORE, ctx.n_tokens, self.rt.tc)
+            if pend is not None:
+                partial, splits, stride = pend
+            else:
+                ops_tensor.flush_pending(y.device, self.rt.tc)
         if keep_rows is None:
-            ops.gated_add(x, g, y, ctx.n_tokens)
+            ops.gated_add(x, g, y, ctx.n_tokens, partial=partial, splits=splits, split_stride=stride)
         else:
-            ops.gated_add(x, g, y, ctx.n_tokens, keep_rows, ctx.tok_seq, ctx.seq_start, ctx.seq_slot, state)
+            ops.gated_add(x, g, y, ctx.n_tokens, keep_rows, ctx.tok_seq, ctx.seq_start, ctx.seq_slot, state,
+                          partial=partial, splits=splits, split_stride=stride)
 
     def resident_tensors(self):
         return [self.proj.w, self.proj.bias]

@@ -126,10 +126,11 @@ class LatentAttention(Part):
     def forward(self, ctx, h, x, view, owns_cache=True):
         self._run(ctx, h, x, view, owns_cache, accumulate=True)
 
-    def produce(self, ctx, h, out, view, owns_cache=True):
-        self._run(ctx, h, out, view, owns_cache, accumulate=False)
+    def produce(self, ctx, h, out, view, owns_cache=True, defer=False):
+        """`defer`: the last product may leave K-split partial sums of `out` for the caller's next kernel."""
+        self._run(ctx, h, out, view, owns_cache, accumulate=False, defer=defer)
 
-    def _run(self, ctx, h, target, view, owns_cache, accumulate):
+    def _run(self, ctx, h, target, view, owns_cache, accumulate, defer=False):
         n = ctx.n_tokens
         names = self._names()
         proj = ctx.buf(names[0], self.q_width + self.rank)
@@ -155,7 +156,7 @@ class LatentAttention(Part):
         if accumulate:
             self.o.accumulate(v, target, n, defer=False)
         else:
-            self.o.store(v, target, n)
+            self.o.store(v, target, n, defer=defer)
 
     def resident_tensors(self):
         return [self.q_dkv.w, self.o.w, self.latent_norm, self.sink, self.uk, self.expand.w]

@@ -84,10 +84,11 @@ class DenseMLP(Part):
         self.up = Linear(tensors["up"], rt, activation=self.activation)
         self.down = Linear(tensors["down"], rt)
 
-    def produce(self, ctx, h, out):
+    def produce(self, ctx, h, out, defer=False):
+        """`defer`: the second product may leave K-split partial sums of `out` for the caller's next kernel."""
         act = ctx.buf(f"dense_act_{self.inner}", self.inner)
         self.up.store_act(h, act, ctx.n_tokens)
-        self.down.store(act, out, ctx.n_tokens)
+        self.down.store(act, out, ctx.n_tokens, defer=defer)
 
     def forward(self, ctx, h, x):
         act = ctx.buf(f"dense_act_{self.inner}", self.inner)

@@ -37,18 +37,21 @@ class _StatefulMixer(Part):
     def forward(self, ctx, h, x, view, owns_cache=True):
         self._run(ctx, h, x, view, accumulate=True)
 
-    def produce(self, ctx, h, out, view, owns_cache=True):
-        self._run(ctx, h, out, view, accumulate=False)
+    def produce(self, ctx, h, out, view, owns_cache=True, defer=False):
+        """`defer`: the last product may leave K-split partial sums of `out` for the caller's next kernel."""
+        self._run(ctx, h, out, view, accumulate=False, defer=defer)
 
-    def _finish(self, proj, a, target, n, accumulate):
+    def _finish(self, proj, a, target, n, accumulate, defer=False):
         if accumulate:
             proj.accumulate(a, target, n, defer=False)
         else:
-            proj.store(a, target, n)
+            proj.store(a, target, n, defer=defer)
 
 
 @MIXERS.register("mingru")
 class MinGRU(_StatefulMixer):
+    CHUNKED_FROM = 128        # rows in the step's longest sequence from which the chunked scan is used
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden, self.width = int(self.params["hidden_size"]), int(self.params["width"])
@@ -77,13 +80,16 @@ class MinGRU(_StatefulMixer):
         self.o = Linear(tensors["o"], rt)
         self.bz, self.bx = tensors["z.b"], tensors["x.b"]
 
-    def _run(self, ctx, h, target, view, accumulate):
+    def _run(self, ctx, h, target, view, accumulate, defer=False):
         n, w = ctx.n_tokens, self.width
         p = ctx.buf(f"mingru_p_{w}", 3 * w, torch.float32)
         s = ctx.buf(f"mingru_s_{w}", w)
         self.zxg.store(h, p, n)
-        ops.mingru_scan(p, self.bz, self.bx, ctx.seq_start, ctx.seq_slot, view.state, s, ctx.n_seqs, w)
-        self._finish(self.o, s, target, n, accumulate)
+        # steps of many rows in the serving engine: runs of a sequence side by side; the 32-bit engine keeps the
+        # row-by-row order, so that its results do not depend on how a prompt was cut
+        chunked = ctx.max_new >= self.CHUNKED_FROM and s.dtype != torch.float32
+        ops.mingru_scan(p, self.bz, self.bx, ctx.seq_start, ctx.seq_slot, view.state, s, ctx.n_seqs, w, chunked)
+        self._finish(self.o, s, target, n, accumulate, defer)
 
     def resident_tensors(self):
         return [self.zxg.w, self.o.w, self.bz, self.bx]
@@ -92,6 +98,7 @@ class MinGRU(_StatefulMixer):
 @MIXERS.register("mamba2")
 class Mamba2(_StatefulMixer):
     MAX_STATE, MAX_TAPS = 256, 16          # the scan kernel's and the convolution kernel's limits
+    CHUNK_ROWS = 256                       # the serving engine walks prompts as runs of this many rows side by side
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -130,13 +137,17 @@ class Mamba2(_StatefulMixer):
         return StateNeed((self.state_floats + self.conv_floats,), torch.float32)
 
     def _names(self):
-        tag = f"{self.proj_width}_{self.inner}"
-        return f"mamba_proj_{tag}", f"mamba_conv_{tag}", f"mamba_y_{tag}", f"mamba_g_{tag}"
+        tag = f"{self.proj_width}_{self.inner}_{self.n_state}"
+        return f"mamba_proj_{tag}", f"mamba_conv_{tag}", f"mamba_y_{tag}", f"mamba_g_{tag}", f"mamba_runs_{tag}"
+
+    def _run_columns(self) -> int:
+        # scratch for the side-by-side runs: room for two runs' states (and decays) per CHUNK_ROWS rows of a step
+        return -(-2 * (self.state_floats + self.heads) // self.CHUNK_ROWS)
 
     def workspace(self):
-        proj, conv, y, g = self._names()
+        proj, conv, y, g, runs = self._names()
         return {proj: (self.proj_width, "f32"), conv: (self.channels, "f32"), y: (self.inner, "f32"),
-                g: (self.inner, "act")}
+                g: (self.inner, "act"), runs: (self._run_columns(), "f32")}
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
@@ -145,7 +156,7 @@ class Mamba2(_StatefulMixer):
         self.conv_w, self.conv_b = tensors["conv"], tensors["conv.b"]
         self.dt_bias, self.a_log, self.d, self.norm = tensors["dt_bias"], tensors["A_log"], tensors["D"], tensors["norm"]
 
-    def _run(self, ctx, h, target, view, accumulate):
+    def _run(self, ctx, h, target, view, accumulate, defer=False):
         n = ctx.n_tokens
         names = self._names()
         proj = ctx.buf(names[0], self.proj_width, torch.float32)
@@ -157,10 +168,20 @@ class Mamba2(_StatefulMixer):
         self.w_in.store(h, proj, n)
         ops.causal_conv_silu(proj, self.inner, self.conv_w, self.conv_b, self.taps, self.channels, ctx.tok_seq,
                              ctx.seq_start, ctx.seq_slot, conv_state, conv, n, ctx.n_seqs)
+        # steps of long prompts in the serving engine: runs of CHUNK_ROWS rows side by side, if the scratch holds
+        # them (it does unless one long prompt comes with many short ones); else, and always in the 32-bit engine,
+        # row by row
+        chunk_rows, max_chunks, scratch = 0, 1, None
+        if g.dtype != torch.float32 and ctx.max_new >= 2 * self.CHUNK_ROWS:
+            runs = ctx.buf(names[4], self._run_columns(), torch.float32).view(-1)
+            most = -(-ctx.max_new // self.CHUNK_ROWS)
+            if ctx.n_seqs * most * (self.state_floats + self.heads) <= runs.numel():
+                chunk_rows, max_chunks, scratch = self.CHUNK_ROWS, most, runs
         ops.mamba2_scan(conv, proj, self.proj_width - self.heads, self.dt_bias, self.a_log, self.d, ctx.seq_start,
-                        ctx.seq_slot, ssm_state, y, ctx.n_seqs, self.heads, self.vdim, self.n_state, self.groups)
+                        ctx.seq_slot, ssm_state, y, ctx.n_seqs, self.heads, self.vdim, self.n_state, self.groups,
+                        chunk_rows, max_chunks, scratch)
         ops.gated_group_rmsnorm(y, proj[:, :self.inner], self.norm, g, n, self.norm_groups, self.eps)
-        self._finish(self.o, g, target, n, accumulate)
+        self._finish(self.o, g, target, n, accumulate, defer)
 
     def resident_tensors(self):
         return [self.w_in.w, self.o.w, self.conv_w, self.conv_b, self.dt_bias, self.a_log, self.d, self.norm]

@@ -247,6 +247,76 @@ def test_mamba2_scan_shapes_and_portions(heads, vdim, N, G):
 
 
 @pytest.mark.gpu
+def test_scans_that_walk_runs_side_by_side():
+    """The kernels for steps of many rows (minGRU: 32 runs a sequence; Mamba-2: runs of 256 rows in three passes)
+    against the plain recurrences, on a batch of a long, a short and a one-row sequence that all carry state
+    from an earlier step."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    lengths, slots, Wd = [700, 45, 1], [2, 0, 3], 70
+    first = [3, 2, 5]                                   # rows of an earlier step, walked row by row
+    total = [a + b for a, b in zip(first, lengths)]
+    p = [torch.randn(n, 3 * Wd, generator=g) for n in total]
+    bz, bu = torch.randn(Wd, generator=g), torch.randn(Wd, generator=g)
+    want = []
+    for ps in p:
+        z = torch.sigmoid(ps[:, :Wd].double() + bz.double())
+        u = ps[:, Wd:2 * Wd].double() + bu.double()
+        cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        S, rows = torch.zeros(Wd, dtype=torch.float64), []
+        for t in range(ps.shape[0]):
+            S = (1 - z[t]) * S + z[t] * cand[t]
+            rows.append(S * pg.silu(ps[t, 2 * Wd:].double()))
+        want.append(torch.stack(rows))
+    state = torch.zeros(4, Wd, device="cuda")
+    for chunked, take, lo in ((False, first, [0, 0, 0]), (True, lengths, first)):
+        _, seq_start, seq_slot = _meta(take, slots)
+        rows = torch.cat([ps[l:l + n] for ps, l, n in zip(p, lo, take)])
+        out = torch.empty(sum(take), Wd, device="cuda")
+        ops.mingru_scan(_dev(rows), _dev(bz), _dev(bu), seq_start, seq_slot, state, out, 3, Wd, chunked)
+        at = 0
+        for s, (l, n) in enumerate(zip(lo, take)):
+            assert (out[at:at + n].cpu().double() - want[s][l:l + n]).abs().max() < 2e-5, (chunked, s)
+            at += n
+    # Mamba-2
+    heads, vdim, N, G = 3, 20, 24, 3
+    inner = heads * vdim
+    conv = [torch.randn(n, inner + 2 * G * N, generator=g) * 0.7 for n in total]
+    raw = [torch.randn(n, heads, generator=g) for n in total]
+    dt_bias, a_log, D = torch.rand(heads, generator=g) * 3 - 3, torch.rand(heads, generator=g) * 2 - 1, torch.randn(heads, generator=g)
+    want = []
+    for cs, rs in zip(conv, raw):
+        dt = torch.nn.functional.softplus(rs.double() + dt_bias.double(), threshold=1e9)
+        x = cs[:, :inner].double().reshape(-1, heads, vdim)
+        B = cs[:, inner:inner + G * N].double().reshape(-1, G, N)
+        C = cs[:, inner + G * N:].double().reshape(-1, G, N)
+        S = torch.zeros(heads, N, vdim, dtype=torch.float64)
+        y = torch.zeros(cs.shape[0], heads, vdim, dtype=torch.float64)
+        for t in range(cs.shape[0]):
+            for h in range(heads):
+                S[h] = torch.exp(-torch.exp(a_log[h].double()) * dt[t, h]) * S[h] + dt[t, h] * torch.outer(B[t, h], x[t, h])
+                y[t, h] = S[h].t() @ C[t, h] + D[h].double() * x[t, h]
+        want.append(y.reshape(-1, inner))
+    sf = heads * N * vdim
+    state = torch.zeros(4, sf, device="cuda")
+    runs = -(-max(lengths) // 256)
+    scratch = torch.full((3 * runs * (sf + heads),), float("nan"), device="cuda")
+    for rows_per_run, take, lo in ((0, first, [0, 0, 0]), (256, lengths, first)):
+        _, seq_start, seq_slot = _meta(take, slots)
+        rc = torch.cat([c[l:l + n] for c, l, n in zip(conv, lo, take)])
+        rr = torch.cat([r[l:l + n] for r, l, n in zip(raw, lo, take)])
+        y = torch.empty(sum(take), inner, device="cuda")
+        ops.mamba2_scan(_dev(rc), _dev(rr), 0, _dev(dt_bias), _dev(a_log), _dev(D), seq_start, seq_slot, state, y, 3,
+                        heads, vdim, N, G, rows_per_run, runs if rows_per_run else 1, scratch if rows_per_run else None)
+        at = 0
+        for s, (l, n) in enumerate(zip(lo, take)):
+            assert (y[at:at + n].cpu().double() - want[s][l:l + n]).abs().max() < 2e-4, (rows_per_run, s)
+            at += n
+    # one more row each, row by row, from the state the runs left
+    assert float(state[1].abs().max()) == 0
+
+
+@pytest.mark.gpu
 def test_gated_group_norm_softcap_pack_and_headwise_product():
     from mdma_b200 import ops
     g = torch.Generator().manual_seed(2)
@@ -546,6 +616,30 @@ def test_long_prompts_on_the_tensor_core_kernels():
         close(out, np.stack([ra[200 + p], rb[90 + p]]), "bfloat16", f"decoded {p}")
     out = eng.step([StepEntry(sa, a[220:], list(range(10))), StepEntry(sb, b[110:], [9])]).cpu().numpy()
     close(out, np.concatenate([ra[220:], rb[119:120]]), "bfloat16", "last portions")
+    eng.check_status()
+
+
+@pytest.mark.gpu
+def test_a_prompt_long_enough_for_the_side_by_side_scans():
+    """bfloat16, one prompt of 640 tokens beside one of 530 (the scans walk them as runs), then decoding from
+    the state that leaves; and the same prompt fed in portions of 100 (row by row) gives the same logits."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of("C", "bfloat16")
+    a, b = ids_of(cfg, 650, 70), ids_of(cfg, 534, 71)
+    ra, rb = ref_of("C", "bfloat16", a), ref_of("C", "bfloat16", b)
+    eng = Engine(d, dtype="bfloat16", max_batch=2, max_context=704, logit_rows=64)
+    sa, sb = eng.acquire(), eng.acquire()
+    wa, wb = [0, 255, 256, 257, 511, 512, 639], [0, 300, 529]
+    out = eng.step([StepEntry(sa, a[:640], wa), StepEntry(sb, b[:530], wb)]).cpu().numpy()
+    close(out, np.concatenate([ra[wa], rb[wb]]), "bfloat16", "long prompts")
+    for p in range(4):
+        out = eng.step([StepEntry(sa, [a[640 + p]], [0]), StepEntry(sb, [b[530 + p]], [0])]).cpu().numpy()
+        close(out, np.stack([ra[640 + p], rb[530 + p]]), "bfloat16", f"decoded {p}")
+    eng.release(sa)
+    sa = eng.acquire()
+    for lo in range(0, 600, 100):
+        out = eng.step([StepEntry(sa, a[lo:lo + 100], [99])]).cpu().numpy()
+        close(out, ra[lo + 99:lo + 100], "bfloat16", f"portion at {lo}")
     eng.check_status()
 
 
