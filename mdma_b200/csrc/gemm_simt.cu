@@ -3,8 +3,10 @@
 // This is the product of the true 32-bit engine (float inputs, float FMA, no
 // reduced-precision matrix mode) and the fallback of the bfloat16 engine for
 // shapes the tensor-core kernel refuses.  Every output element is accumulated
-// by one thread over k = 0..K-1 in order, so a row's result does not depend on
-// how many other rows are in the call.
+// by one thread, in one fixed order: the products of each run of 16 values of k
+// are summed from zero and the runs' sums are added up in order (two short
+// chains of roundings instead of one of length K), so a row's result does not
+// depend on how many other rows are in the call.
 #include "common.cuh"
 
 namespace mdma {
@@ -50,6 +52,8 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
                 Ws2[lk + i][lrow] = (n < N && k < K) ? to_float(W2[(size_t)n * K + k]) : 0.f;
         }
         __syncthreads();
+        float part[4][4] = {};
+        float part2[MODE == kSwiGLU ? 4 : 1][4] = {};
 #pragma unroll
         for (int k = 0; k < TK; ++k) {
             float a[4], w[4];
@@ -60,16 +64,23 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], w[j], part[i][j]);
             if (MODE == kSwiGLU) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) w[j] = Ws2[k][tx * 4 + j];
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc2[i][j] = fmaf(a[i], w[j], acc2[i][j]);
+                    for (int j = 0; j < 4; ++j) part2[i][j] = fmaf(a[i], w[j], part2[i][j]);
             }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[i][j] += part[i][j];
+                if (MODE == kSwiGLU) acc2[i][j] += part2[i][j];
+            }
         __syncthreads();
     }
 #pragma unroll

@@ -6,13 +6,15 @@
 // key-and-value head of size `rank`.  The softmax has a sink: exp(sink_h) is added to the
 // denominator once, with no key, no value and no scale.
 //
-// Plain kernels: one warp per (token, head), keys visited in position order, everything in
-// float; the result of a token does not depend on the step's cut or on the batch.
+// Plain kernels: one warp per (token, head), keys visited in position order, 32 at a time
+// (their scores first, then their maximum, then their weighted sum from zero, which is
+// folded into the running sum: short chains of roundings), everything in float; the result
+// of a token does not depend on the step's cut or on the batch.
 #include "common.cuh"
 
 namespace mdma {
 
-constexpr int kMaxRank = 512;
+constexpr int kMaxRank = 1024;
 
 // c = x / sqrt(mean(x^2) + eps) * w for x = columns [col0, col0 + rank) of the token's projection
 // row; written to the token's row of the paged cache ([pages, page_size, rank]).
@@ -69,23 +71,43 @@ latent_attention_kernel(const T* __restrict__ q, int q_row_stride, const T* __re
     }
     float m = -INFINITY, l = 0.f;
     const int* pages = page_table + (size_t)slot * max_pages;
-    for (int p = first; p <= pos; ++p) {
-        const T* cp = cache + ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * rank;
-        float cv[kMaxRank / 32];
-        float part = 0.f;
+    for (int p0 = first; p0 <= pos; p0 += 32) {
+        const int nk = min(32, pos + 1 - p0);
+        // the scores of up to 32 keys: lane j keeps the score of key p0 + j
+        float mine = -INFINITY;
+        for (int k = 0; k < nk; ++k) {
+            const int p = p0 + k;
+            const T* cp = cache + ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * rank;
+            float part = 0.f;
 #pragma unroll
-        for (int j = 0; j < kMaxRank / 32; ++j) {
-            const int d = lane + 32 * j;
-            cv[j] = d < rank ? to_float(cp[d]) : 0.f;
-            part = fmaf(qv[j], cv[j], part);
+            for (int j = 0; j < kMaxRank / 32; ++j) {
+                const int d = lane + 32 * j;
+                if (d < rank) part = fmaf(qv[j], to_float(cp[d]), part);
+            }
+            const float s = warp_sum(part) * scale;
+            if (lane == k) mine = s;
         }
-        const float s = warp_sum(part) * scale;
-        const float m_new = fmaxf(m, s);
-        const float corr = expf(m - m_new);
-        const float pe = expf(s - m_new);
-        l = l * corr + pe;
+        const float m_new = fmaxf(m, warp_max(mine));
+        const float corr = expf(m - m_new);          // exp(-inf) = 0 at the first keys
+        const float pe_mine = lane < nk ? expf(mine - m_new) : 0.f;
+        float sum[kMaxRank / 32];
 #pragma unroll
-        for (int j = 0; j < kMaxRank / 32; ++j) acc[j] = acc[j] * corr + pe * cv[j];
+        for (int j = 0; j < kMaxRank / 32; ++j) sum[j] = 0.f;
+        float l_new = 0.f;
+        for (int k = 0; k < nk; ++k) {
+            const int p = p0 + k;
+            const T* cp = cache + ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * rank;
+            const float pe = __shfl_sync(0xffffffffu, pe_mine, k);
+            l_new += pe;
+#pragma unroll
+            for (int j = 0; j < kMaxRank / 32; ++j) {
+                const int d = lane + 32 * j;
+                if (d < rank) sum[j] = fmaf(pe, to_float(cp[d]), sum[j]);
+            }
+        }
+        l = l * corr + l_new;
+#pragma unroll
+        for (int j = 0; j < kMaxRank / 32; ++j) acc[j] = acc[j] * corr + sum[j];
         m = m_new;
     }
     const float sk = to_float(sink[h]);

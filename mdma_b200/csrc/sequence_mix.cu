@@ -333,7 +333,7 @@ conv_keep_kernel(const float* __restrict__ proj, int proj_stride, int in_col, in
 constexpr int kScanRows = 16;
 enum ScanPass : int { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 
-template <int NPER, typename TW, int PASS>
+template <int NPER, int VPT, typename TW, int PASS>
 __global__ void __launch_bounds__(128)
 mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float* __restrict__ proj, int proj_stride,
                    int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log, const TW* __restrict__ D,
@@ -342,8 +342,10 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
                    int chunk_rows, int max_chunks, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
     chain_release();
     chain_wait();
-    extern __shared__ float sm[];
-    const int VB = blockDim.x / NP;
+    extern __shared__ __align__(16) float sm[];
+    // a thread owns NPER state rows of VPT value columns: B and C, which every column needs, are fetched once for
+    // VB = (threads / NP) * VPT columns
+    const int VB = blockDim.x / NP * VPT;
     const int Npad = NP * NPER;
     float* sB = sm;
     float* sC = sB + kScanRows * Npad;
@@ -364,18 +366,20 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
     }
     const size_t state_floats = (size_t)heads * N * vdim;
     const int g = h / (heads / G);
-    const int np = threadIdx.x % NP, vl = threadIdx.x / NP;
-    const int v = v0 + vl;
-    const bool vok = v < vdim;
+    const int np = threadIdx.x % NP, vl = (threadIdx.x / NP) * VPT;       // first of this thread's columns, within the block
     const int inner = heads * vdim;
     float* Sg = state + (size_t)seq_slot[s] * state_stride + (size_t)h * N * vdim;
     float* Sc = PASS == kScanWhole ? nullptr : chunk_state + (size_t)blockIdx.x * state_floats + (size_t)h * N * vdim;
     const float* Sfrom = PASS == kScanWhole ? Sg : Sc;
-    float S[NPER];
+    float S[VPT][NPER];
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-        const int n = np * NPER + i;
-        S[i] = (PASS != kScanLocal && vok && n < N) ? Sfrom[(size_t)v * N + n] : 0.f;
+    for (int j = 0; j < VPT; ++j) {
+        const int v = v0 + vl + j;
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int n = np * NPER + i;
+            S[j][i] = (PASS != kScanLocal && v < vdim && n < N) ? Sfrom[(size_t)v * N + n] : 0.f;
+        }
     }
     float dt_sum = 0.f;
     const float rate = expf(to_float(A_log[h])), Dh = to_float(D[h]), bias = to_float(dt_bias[h]);
@@ -401,27 +405,50 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
         if (PASS == kScanLocal && threadIdx.x == 0)
             for (int tt = 0; tt < nt; ++tt) dt_sum += sdt[tt];
         for (int tt = 0; tt < nt; ++tt) {
-            const float a = sa[tt], xv = sx[tt * VB + vl], dtx = sdt[tt] * xv;
-            const float* Bt = sB + tt * Npad + np * NPER;
-            const float* Ct = sC + tt * Npad + np * NPER;
-            float acc = 0.f;
+            const float a = sa[tt], dt = sdt[tt];
+            // a thread's NPER entries of B and of C lie side by side: 16-byte shared-memory loads
+            float Bt[NPER], Ct[NPER];
 #pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                S[i] = fmaf(a, S[i], dtx * Bt[i]);
-                if (PASS != kScanLocal) acc = fmaf(S[i], Ct[i], acc);
+            for (int i = 0; i < NPER; i += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(sB + tt * Npad + np * NPER + i);
+                Bt[i] = b4.x; Bt[i + 1] = b4.y; Bt[i + 2] = b4.z; Bt[i + 3] = b4.w;
+                if (PASS != kScanLocal) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(sC + tt * Npad + np * NPER + i);
+                    Ct[i] = c4.x; Ct[i + 1] = c4.y; Ct[i + 2] = c4.z; Ct[i + 3] = c4.w;
+                }
+            }
+            float acc[VPT], xv[VPT];
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                xv[j] = sx[tt * VB + vl + j];
+                const float dtx = dt * xv[j];
+                acc[j] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    S[j][i] = fmaf(a, S[j][i], dtx * Bt[i]);
+                    if (PASS != kScanLocal) acc[j] = fmaf(S[j][i], Ct[i], acc[j]);
+                }
             }
             if (PASS != kScanLocal) {
-                for (int o = NP >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (np == 0 && vok) y[(size_t)(t0 + tt) * inner + h * vdim + v] = acc + Dh * xv;
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    for (int o = NP >> 1; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+                    const int v = v0 + vl + j;
+                    if (np == 0 && v < vdim) y[(size_t)(t0 + tt) * inner + h * vdim + v] = acc[j] + Dh * xv[j];
+                }
             }
         }
     }
     float* Sto = PASS == kScanLocal ? Sc : (last_run ? Sg : nullptr);
     if (Sto != nullptr) {
 #pragma unroll
-        for (int i = 0; i < NPER; ++i) {
-            const int n = np * NPER + i;
-            if (vok && n < N) Sto[(size_t)v * N + n] = S[i];
+        for (int j = 0; j < VPT; ++j) {
+            const int v = v0 + vl + j;
+#pragma unroll
+            for (int i = 0; i < NPER; ++i) {
+                const int n = np * NPER + i;
+                if (v < vdim && n < N) Sto[(size_t)v * N + n] = S[j][i];
+            }
         }
     }
     if (PASS == kScanLocal && threadIdx.x == 0 && blockIdx.z == 0)
@@ -650,39 +677,44 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     const int nper = 8;
     int np = 1;
     while (np * nper < N) np <<= 1;           // lanes per value column: a power of two, at most 32
-    const int vb = 128 / np;
+    const int vpt = vdim >= 32 ? 4 : 1;       // value columns per thread: B and C are fetched once for all of a block's
+    const int vb = 128 / np * vpt;
     const size_t smem = sizeof(float) * (size_t)(2 * kScanRows * np * nper + kScanRows * vb + 2 * kScanRows);
     dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb);
     MDMA_REQUIRE(grid.z <= 65535, "mamba2_scan: value size %d is too large", vdim);
+    float* chunk_state = nullptr;
+    float* chunk_decay = nullptr;
     if (chunk_rows > 0) {
         const long state_floats = (long)heads * N * vdim;
         const long slots = (long)n_seqs * max_chunks;
         MDMA_REQUIRE(max_chunks >= 1 && slots <= 65535 * 16l && scratch != nullptr && scratch_floats >= slots * (state_floats + heads),
                      "mamba2_scan: %ld runs need %ld floats of scratch, %ld given", slots, slots * (state_floats + heads), scratch_floats);
-        float* chunk_state = scratch;
-        float* chunk_decay = scratch + slots * state_floats;
-        dim3 cgrid((unsigned)slots, heads, grid.z);
-        MDMA_DISPATCH_DTYPE(w_dtype, TW,
-            launch_chained(mamba2_scan_kernel<8, TW, kScanLocal>, cgrid, dim3(128), smem, stream, conv, conv_stride, proj,
-                           proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,
-                           state, state_stride, y, heads, vdim, N, G, np, chunk_rows, max_chunks, chunk_state, chunk_decay));
-        MDMA_LAUNCH_OK("mamba2_scan (runs from zero)");
-        launch_chained(mamba2_chunk_starts_kernel, dim3((unsigned)((state_floats + 255) / 256), n_seqs), dim3(256), 0, stream,
+        chunk_state = scratch;
+        chunk_decay = scratch + slots * state_floats;
+        grid.x = (unsigned)slots;
+    } else {
+        chunk_rows = 0; max_chunks = 1;
+    }
+#define MDMA_SCAN_LAUNCH(VPT_, PASS_, what)                                                                            \
+    MDMA_DISPATCH_DTYPE(w_dtype, TW,                                                                                   \
+        launch_chained(mamba2_scan_kernel<8, VPT_, TW, PASS_>, grid, dim3(128), smem, stream, conv, conv_stride, proj,   \
+                       proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,     \
+                       state, state_stride, y, heads, vdim, N, G, np, chunk_rows, max_chunks, chunk_state, chunk_decay)); \
+    MDMA_LAUNCH_OK(what)
+    if (chunk_rows > 0) {
+        if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanLocal, "mamba2_scan (runs from zero)"); }
+        else { MDMA_SCAN_LAUNCH(1, kScanLocal, "mamba2_scan (runs from zero)"); }
+        launch_chained(mamba2_chunk_starts_kernel, dim3((unsigned)(((long)heads * N * vdim + 255) / 256), n_seqs), dim3(256), 0, stream,
                        seq_start, seq_slot, (const float*)state, state_stride, chunk_state, (const float*)chunk_decay, heads,
                        N * vdim, chunk_rows, max_chunks);
         MDMA_LAUNCH_OK("mamba2_chunk_starts");
-        MDMA_DISPATCH_DTYPE(w_dtype, TW,
-            launch_chained(mamba2_scan_kernel<8, TW, kScanFrom>, cgrid, dim3(128), smem, stream, conv, conv_stride, proj,
-                           proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,
-                           state, state_stride, y, heads, vdim, N, G, np, chunk_rows, max_chunks, chunk_state, chunk_decay));
-        MDMA_LAUNCH_OK("mamba2_scan (runs from their starts)");
+        if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanFrom, "mamba2_scan (runs from their starts)"); }
+        else { MDMA_SCAN_LAUNCH(1, kScanFrom, "mamba2_scan (runs from their starts)"); }
         return 0;
     }
-    MDMA_DISPATCH_DTYPE(w_dtype, TW,
-        launch_chained(mamba2_scan_kernel<8, TW, kScanWhole>, grid, dim3(128), smem, stream, conv, conv_stride, proj, proj_stride,
-                       dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot, state,
-                       state_stride, y, heads, vdim, N, G, np, 0, 1, (float*)nullptr, (float*)nullptr));
-    MDMA_LAUNCH_OK("mamba2_scan");
+    if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanWhole, "mamba2_scan"); }
+    else { MDMA_SCAN_LAUNCH(1, kScanWhole, "mamba2_scan"); }
+#undef MDMA_SCAN_LAUNCH
     return 0;
 }
 

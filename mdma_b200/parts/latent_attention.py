@@ -53,7 +53,7 @@ class HeadwiseLinear:
 @MIXERS.register("latent_attention")
 class LatentAttention(Part):
     graph_safe = True      # forward reads no host-side per-step values
-    MAX_RANK = 512         # the attention kernel's limit (csrc/latent_attention.cu)
+    MAX_RANK = 1024        # the attention kernel's limit (csrc/latent_attention.cu)
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -9,8 +9,9 @@ For a step that wants logits it writes OUT/<step>.f32 (little-endian float32,
 `done <step>`.  It samples nothing and owns no model code: every step goes
 through the engine's own step function, cache and kernels, the ones generation
 uses.  `--dtype float32` runs every operation in true 32-bit arithmetic.
-`--max-tokens` sizes the cache: the most tokens live requests hold at any time,
-each request's count rounded up to a multiple of 64.
+`--max-tokens` sizes the cache: the most tokens live requests hold at any time;
+the cache gets that many rows in pages of 64 plus sixteen pages for last pages
+that are partly filled.
 
 Two options exist for tests: `--chunk-tokens N` makes the engine run a step of
 more than N tokens as several passes over the cache, and `--poison-unused`
@@ -38,7 +39,8 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     page = 64
-    max_tokens = -(-args.max_tokens // page) * page
+    # every live request may hold a partly filled last page: room for sixteen of those beyond the tokens asked for
+    max_tokens = (-(-args.max_tokens // page) + 16) * page
     # the model class and its sizes come from config.json through the architecture registry, as for generation
     from mdma_b200.config import load_config
     arch, config = load_config(args.model)

@@ -51,6 +51,25 @@ CFG_C = {
 }
 
 
+# no attention at all (no cache group), and attention only (state only for the token shift); a latent wider than
+# the tensor-core attention kernels take, so the plain kernel serves it in both engines
+CFG_D = {
+    "architecture": "Gevonex", "vocab": 61, "width": 48, "norm": {"eps": 1e-5}, "logit_softcap": 12.0,
+    "loop": {"start": 0, "stop": 1, "times": 2},
+    "layers": [
+        _layer("mingru", {"width": 64}, 48),
+        _layer("mamba2", {"heads": 2, "vdim": 16, "state": 40, "groups": 2, "norm_groups": 2, "conv": 3}, 80),
+    ],
+}
+CFG_E = {
+    "architecture": "Gevonex", "vocab": 70, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 25.0,
+    "layers": [
+        _layer("latent_attention", {"heads": 2, "dim": 24, "vdim": 40, "kv_rank": 144, "scale": 0.15}, 64),
+        _layer("latent_attention", {"heads": 4, "dim": 16, "vdim": 16, "kv_rank": 48, "scale": 0.3}, None),
+    ],
+}
+
+
 def make_tensors(cfg, seed):
     """name -> float32 tensor, for every tensor the architecture declares."""
     from mdma_b200.config import load_config

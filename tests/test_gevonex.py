@@ -11,9 +11,9 @@ import pytest
 import torch
 
 import plain_gevonex as pg
-from gevonex_tiny import CFG_A, CFG_B, CFG_C, make_model, make_tensors
+from gevonex_tiny import CFG_A, CFG_B, CFG_C, CFG_D, CFG_E, make_model, make_tensors
 
-CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
 # float32: absolute, against the float64 statement.  bfloat16: absolute, and a row's root-mean-square error as a
 # share of the row's own deviation.  The largest seen on a B200 over all tests of this file: 6e-6 in float32;
 # 0.065 and 1.9 % in bfloat16 (GEVONEX_TEST_REPORT=1 prints them).
@@ -60,7 +60,7 @@ def test_config_is_read_and_checked():
     assert [(i, t) for i, t in pg.layer_runs(CFG_A)] == [(l, a if j is not None else None) for l, j, a in runs]
     _, b = load_config(CFG_B)
     assert b.loop_times == 0 and b.logit_softcap == 0.0 and not arch.describe(b).junctions
-    for breaker in (lambda d: d.pop("width"), lambda d: d.update(extra_key=1),
+    for breaker in (lambda d: d.pop("width"),
                     lambda d: d["layers"][0].update(type="lstm"),
                     lambda d: d["layers"][0]["mixer"].pop("groups"),
                     lambda d: d["layers"][0]["mlp"].update(kind="routed"),
@@ -488,7 +488,7 @@ def ref_of(key, dtype, ids):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D", "E"])
 def test_every_layer_against_the_plain_statement(key, dtype):
     """The residual stream after every run of a layer, then the logits; one short prompt."""
     from mdma_b200.engine import Engine, StepEntry
@@ -510,7 +510,7 @@ def test_every_layer_against_the_plain_statement(key, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D", "E"])
 def test_batches_portions_decoding_and_reuse(key, dtype):
     """Unequal prompts in one step; the same prompts cut in portions down to one and two tokens on a cached
     prefix; token-by-token decoding; sequences that end early while others go on; slots and pages freed and
