@@ -333,16 +333,19 @@ conv_keep_kernel(const float* __restrict__ proj, int proj_stride, int in_col, in
 constexpr int kScanRows = 16;
 enum ScanPass : int { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 
-template <int NPER, int VPT, typename TW, int PASS>
+// NPT: the lanes that share a value column, when known at compile time (the common state sizes: loops unroll and
+// the index arithmetic folds), or 0: the run-time value `np_lanes` is used.
+template <int NPER, int VPT, int NPT, typename TW, int PASS>
 __global__ void __launch_bounds__(128)
 mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float* __restrict__ proj, int proj_stride,
                    int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log, const TW* __restrict__ D,
                    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, float* __restrict__ state,
-                   long state_stride, float* __restrict__ y, int heads, int vdim, int N, int G, int NP,
+                   long state_stride, float* __restrict__ y, int heads, int vdim, int N, int G, int np_lanes,
                    int chunk_rows, int max_chunks, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(16) float sm[];
+    const int NP = NPT > 0 ? NPT : np_lanes;
     // a thread owns NPER state rows of VPT value columns: B and C, which every column needs, are fetched once for
     // VB = (threads / NP) * VPT columns
     const int VB = blockDim.x / NP * VPT;
@@ -432,6 +435,7 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
             if (PASS != kScanLocal) {
 #pragma unroll
                 for (int j = 0; j < VPT; ++j) {
+#pragma unroll
                     for (int o = NP >> 1; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
                     const int v = v0 + vl + j;
                     if (np == 0 && v < vdim) y[(size_t)(t0 + tt) * inner + h * vdim + v] = acc[j] + Dh * xv[j];
@@ -509,17 +513,17 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, int y_stride, const floa
             const int e = i * blockDim.x + threadIdx.x;
             if (e < size) out[(size_t)t * width + base + e] = from_float<TO>(v[i] * scale * to_float(w[base + e]));
         }
-        return;
-    }
-    for (int e = threadIdx.x; e < size; e += blockDim.x) {
-        const float v = yr[e] * silu_f(zr[e]);
-        ss += v * v;
-    }
-    ss = block_sum(ss, scratch);
-    const float scale = 1.0f / sqrtf(ss / (float)size + eps);
-    for (int e = threadIdx.x; e < size; e += blockDim.x) {
-        const float v = yr[e] * silu_f(zr[e]);
-        out[(size_t)t * width + base + e] = from_float<TO>(v * scale * to_float(w[base + e]));
+    } else {
+        for (int e = threadIdx.x; e < size; e += blockDim.x) {
+            const float v = yr[e] * silu_f(zr[e]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)size + eps);
+        for (int e = threadIdx.x; e < size; e += blockDim.x) {
+            const float v = yr[e] * silu_f(zr[e]);
+            out[(size_t)t * width + base + e] = from_float<TO>(v * scale * to_float(w[base + e]));
+        }
     }
 }
 
@@ -695,12 +699,17 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     } else {
         chunk_rows = 0; max_chunks = 1;
     }
-#define MDMA_SCAN_LAUNCH(VPT_, PASS_, what)                                                                            \
+#define MDMA_SCAN_LAUNCH_NP(VPT_, NPT_, PASS_, what)                                                                   \
     MDMA_DISPATCH_DTYPE(w_dtype, TW,                                                                                   \
-        launch_chained(mamba2_scan_kernel<8, VPT_, TW, PASS_>, grid, dim3(128), smem, stream, conv, conv_stride, proj,   \
-                       proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,     \
+        launch_chained(mamba2_scan_kernel<8, VPT_, NPT_, TW, PASS_>, grid, dim3(128), smem, stream, conv, conv_stride,   \
+                       proj, proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot, \
                        state, state_stride, y, heads, vdim, N, G, np, chunk_rows, max_chunks, chunk_state, chunk_decay)); \
     MDMA_LAUNCH_OK(what)
+#define MDMA_SCAN_LAUNCH(VPT_, PASS_, what)                                                                            \
+    if (np == 4) { MDMA_SCAN_LAUNCH_NP(VPT_, 4, PASS_, what); }                                                          \
+    else if (np == 8) { MDMA_SCAN_LAUNCH_NP(VPT_, 8, PASS_, what); }                                                     \
+    else if (np == 16) { MDMA_SCAN_LAUNCH_NP(VPT_, 16, PASS_, what); }                                                   \
+    else { MDMA_SCAN_LAUNCH_NP(VPT_, 0, PASS_, what); }
     if (chunk_rows > 0) {
         if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanLocal, "mamba2_scan (runs from zero)"); }
         else { MDMA_SCAN_LAUNCH(1, kScanLocal, "mamba2_scan (runs from zero)"); }
@@ -715,6 +724,7 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanWhole, "mamba2_scan"); }
     else { MDMA_SCAN_LAUNCH(1, kScanWhole, "mamba2_scan"); }
 #undef MDMA_SCAN_LAUNCH
+#undef MDMA_SCAN_LAUNCH_NP
     return 0;
 }
 
