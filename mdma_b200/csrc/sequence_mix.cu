@@ -28,9 +28,42 @@ __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
+// Row kernels take VEC = 4 consecutive columns a thread (16-byte accesses of the float rows, 8-byte ones of
+// bfloat16 rows) when the width and every row pitch are multiples of 4, else one.
+template <int VEC, typename T> struct RowVec;
+template <typename T> struct RowVec<1, T> {
+    static __device__ __forceinline__ void load(const T* p, float* v) { v[0] = to_float(p[0]); }
+    static __device__ __forceinline__ void store(T* p, const float* v) { p[0] = from_float<T>(v[0]); }
+};
+template <> struct RowVec<4, float> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct RowVec<4, __nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+        v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 q;
+        q.x = *reinterpret_cast<uint32_t*>(&lo); q.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = q;
+    }
+};
+#define MDMA_ROW_LOOP(e, width, VEC) \
+    for (int e = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; e < width; e += gridDim.y * blockDim.x * VEC)
+
 // ---------------------------------------------------------------- dynamic tanh
 // y[r,:] = tanh(alpha * x[src,:]) * w + b, src = rows[r] or r.  No sum over the row.
-template <typename TO, typename TW>
+template <typename TO, typename TW, int VEC>
 __global__ void __launch_bounds__(256)
 dyt_norm_kernel(const float* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                 const TW* __restrict__ alpha, const int* __restrict__ rows, TO* __restrict__ y, int width) {
@@ -40,15 +73,22 @@ dyt_norm_kernel(const float* __restrict__ x, const TW* __restrict__ w, const TW*
     const float a = to_float(alpha[0]);
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
     TO* yr = y + (size_t)r * width;
-    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x)
-        yr[e] = from_float<TO>(tanhf(a * xr[e]) * to_float(w[e]) + to_float(b[e]));
+    MDMA_ROW_LOOP(e, width, VEC) {
+        float xv[VEC], wv[VEC], bv[VEC], out[VEC];
+        RowVec<VEC, float>::load(xr + e, xv);
+        RowVec<VEC, TW>::load(w + e, wv);
+        RowVec<VEC, TW>::load(b + e, bv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) out[i] = tanhf(a * xv[i]) * wv[i] + bv[i];
+        RowVec<VEC, TO>::store(yr + e, out);
+    }
 }
 
 // The same with the token shift behind it: h = dyt(x[t]) and hs = h + (h' - h) * mu, h' the h of the
 // row before in the same sequence (recomputed from x, which costs nothing for a norm without sums) or,
 // for a sequence's first row of the step, the kept one.  Both h and h' are rounded to the activation
 // type first, so that the kept value and the recomputed one are the same number.
-template <typename TO, typename TW>
+template <typename TO, typename TW, int VEC>
 __global__ void __launch_bounds__(256)
 dyt_shift_kernel(const float* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                  const TW* __restrict__ alpha, const TW* __restrict__ mu, const int* __restrict__ tok_seq,
@@ -62,12 +102,21 @@ dyt_shift_kernel(const float* __restrict__ x, const TW* __restrict__ w, const TW
     const float a = to_float(alpha[0]);
     const float* xr = x + (size_t)t * width;
     const float* prev = first ? state + (size_t)seq_slot[s] * state_stride : xr - width;
-    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) {
-        const float we = to_float(w[e]), be = to_float(b[e]);
-        const float cur = to_float(from_float<TO>(tanhf(a * xr[e]) * we + be));
-        const float before = first ? prev[e] : to_float(from_float<TO>(tanhf(a * prev[e]) * we + be));
-        h[(size_t)t * width + e] = from_float<TO>(cur);
-        hs[(size_t)t * width + e] = from_float<TO>(cur + (before - cur) * to_float(mu[e]));
+    MDMA_ROW_LOOP(e, width, VEC) {
+        float xv[VEC], pv[VEC], wv[VEC], bv[VEC], mv[VEC], cur[VEC], shifted[VEC];
+        RowVec<VEC, float>::load(xr + e, xv);
+        RowVec<VEC, float>::load(prev + e, pv);
+        RowVec<VEC, TW>::load(w + e, wv);
+        RowVec<VEC, TW>::load(b + e, bv);
+        RowVec<VEC, TW>::load(mu + e, mv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            cur[i] = to_float(from_float<TO>(tanhf(a * xv[i]) * wv[i] + bv[i]));
+            const float before = first ? pv[i] : to_float(from_float<TO>(tanhf(a * pv[i]) * wv[i] + bv[i]));
+            shifted[i] = cur[i] + (before - cur[i]) * mv[i];
+        }
+        RowVec<VEC, TO>::store(h + (size_t)t * width + e, cur);
+        RowVec<VEC, TO>::store(hs + (size_t)t * width + e, shifted);
     }
 }
 
@@ -109,7 +158,7 @@ keep_last_rows_kernel(const T* __restrict__ rows, const int* __restrict__ seq_st
 // x[t,:] += sigmoid(g[t,:]) * y[t,:].  With `keep_rows` the rows of it that end a sequence go to
 // the state as well (the token shift's kept row), which saves a launch.  With `splits` > 0, y is the sum of
 // that many partial results [split][row][width] (a K-split product whose reduction is done here).
-template <typename TG, typename TK>
+template <typename TG, typename TK, int VEC>
 __global__ void __launch_bounds__(256)
 gated_add_kernel(float* __restrict__ x, const TG* __restrict__ g, const float* __restrict__ y,
                  const float* __restrict__ partial, int splits, size_t split_stride, int width,
@@ -119,23 +168,36 @@ gated_add_kernel(float* __restrict__ x, const TG* __restrict__ g, const float* _
     chain_wait();
     const int t = blockIdx.x;
     const size_t o = (size_t)t * width;
-    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x)
-    {
+    MDMA_ROW_LOOP(e, width, VEC) {
         // y is either complete or still the K-split partial sums of the product that made it, added up here in split order
-        float v;
+        float v[VEC], xv[VEC], gv[VEC];
         if (splits > 0) {
-            v = 0.f;
-            for (int sp = 0; sp < splits; ++sp) v += partial[(size_t)sp * split_stride + o + e];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+            for (int sp = 0; sp < splits; ++sp) {
+                float pv[VEC];
+                RowVec<VEC, float>::load(partial + (size_t)sp * split_stride + o + e, pv);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) v[i] += pv[i];
+            }
         } else {
-            v = y[o + e];
+            RowVec<VEC, float>::load(y + o + e, v);
         }
-        x[o + e] = x[o + e] + sigmoid_f(to_float(g[o + e])) * v;
+        RowVec<VEC, float>::load(x + o + e, xv);
+        RowVec<VEC, TG>::load(g + o + e, gv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) xv[i] = xv[i] + sigmoid_f(gv[i]) * v[i];
+        RowVec<VEC, float>::store(x + o + e, xv);
     }
     if (keep_rows != nullptr) {
         const int s = tok_seq[t];
         if (t == seq_start[s + 1] - 1) {
             float* kept = state + (size_t)seq_slot[s] * state_stride;
-            for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) kept[e] = to_float(keep_rows[o + e]);
+            MDMA_ROW_LOOP(e, width, VEC) {
+                float kv[VEC];
+                RowVec<VEC, TK>::load(keep_rows + o + e, kv);
+                RowVec<VEC, float>::store(kept + e, kv);
+            }
         }
     }
 }
@@ -540,9 +602,15 @@ int mdma_dyt_norm(const float* x, const void* w, const void* b, const void* alph
                   void* y, int y_dtype, int n_rows, int width, cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "dyt_norm: bad sizes");
     if (n_rows == 0) return 0;
-    MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
-        launch_chained(dyt_norm_kernel<TO, TW>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TW*)w, (const TW*)b,
-                       (const TW*)alpha, rows, (TO*)y, width));
+    if (width % 4 == 0) {
+        MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
+            launch_chained(dyt_norm_kernel<TO, TW, 4>, dim3(n_rows, column_parts(width / 4)), dim3(256), 0, stream, x, (const TW*)w,
+                           (const TW*)b, (const TW*)alpha, rows, (TO*)y, width));
+    } else {
+        MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
+            launch_chained(dyt_norm_kernel<TO, TW, 1>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TW*)w,
+                           (const TW*)b, (const TW*)alpha, rows, (TO*)y, width));
+    }
     MDMA_LAUNCH_OK("dyt_norm");
     return 0;
 }
@@ -552,10 +620,17 @@ int mdma_dyt_shift(const float* x, const void* w, const void* b, const void* alp
                    void* h, void* hs, int y_dtype, int n_rows, int width, cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0 && state_stride >= width, "dyt_shift: bad sizes");
     if (n_rows == 0) return 0;
-    MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
-        launch_chained(dyt_shift_kernel<TO, TW>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TW*)w, (const TW*)b,
-                       (const TW*)alpha, (const TW*)mu, tok_seq, seq_start, seq_slot, state, state_stride,
-                       (TO*)h, (TO*)hs, width));
+    if (width % 4 == 0 && state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0) {
+        MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
+            launch_chained(dyt_shift_kernel<TO, TW, 4>, dim3(n_rows, column_parts(width / 4)), dim3(256), 0, stream, x, (const TW*)w,
+                           (const TW*)b, (const TW*)alpha, (const TW*)mu, tok_seq, seq_start, seq_slot, state, state_stride,
+                           (TO*)h, (TO*)hs, width));
+    } else {
+        MDMA_DISPATCH_2(y_dtype, TO, w_dtype, TW,
+            launch_chained(dyt_shift_kernel<TO, TW, 1>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TW*)w,
+                           (const TW*)b, (const TW*)alpha, (const TW*)mu, tok_seq, seq_start, seq_slot, state, state_stride,
+                           (TO*)h, (TO*)hs, width));
+    }
     MDMA_LAUNCH_OK("dyt_shift");
     return 0;
 }
@@ -590,9 +665,19 @@ int mdma_gated_add(float* x, const void* g, int g_dtype, const float* y, const f
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "gated_add: bad sizes");
     MDMA_REQUIRE(keep_rows == nullptr || (state != nullptr && state_stride >= width), "gated_add: no place for the kept rows");
     if (n_rows == 0) return 0;
-    MDMA_DISPATCH_2(g_dtype, TG, keep_dtype, TK,
-        launch_chained(gated_add_kernel<TG, TK>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TG*)g, y, partial,
-                       partial ? splits : 0, (size_t)split_stride, width, (const TK*)keep_rows, tok_seq, seq_start, seq_slot, state, state_stride));
+    const bool vec = width % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)partial & 15) == 0 &&
+                     (keep_rows == nullptr || (state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0));
+    if (vec) {
+        MDMA_DISPATCH_2(g_dtype, TG, keep_dtype, TK,
+            launch_chained(gated_add_kernel<TG, TK, 4>, dim3(n_rows, column_parts(width / 4)), dim3(256), 0, stream, x, (const TG*)g, y,
+                           partial, partial ? splits : 0, (size_t)split_stride, width, (const TK*)keep_rows, tok_seq, seq_start,
+                           seq_slot, state, state_stride));
+    } else {
+        MDMA_DISPATCH_2(g_dtype, TG, keep_dtype, TK,
+            launch_chained(gated_add_kernel<TG, TK, 1>, dim3(n_rows, column_parts(width)), dim3(256), 0, stream, x, (const TG*)g, y,
+                           partial, partial ? splits : 0, (size_t)split_stride, width, (const TK*)keep_rows, tok_seq, seq_start,
+                           seq_slot, state, state_stride));
+    }
     MDMA_LAUNCH_OK("gated_add");
     return 0;
 }
