@@ -263,12 +263,13 @@ mingru_scan_kernel(const float* __restrict__ p, int p_stride, const TW* __restri
 }
 
 // The same recurrence for steps that bring many rows per sequence: it is linear in S (S_t = a_t S_(t-1) + b_t with
-// a = 1 - z, b = z * candidate), so a sequence's rows are cut into kGruChunks runs; a thread walks one run of one
+// a = 1 - z, b = z * candidate), so a sequence's rows are cut into kGruChunks (128) runs; a thread walks one run of one
 // channel from zero and keeps the run's product of a and its last value, the runs' starting values follow from
 // those in order, and every run is walked again from its starting value, this time writing the outputs.  The
 // association of the products differs from the row-by-row kernel's, so results agree to rounding, not to the bit:
 // the serving engine uses this kernel, the 32-bit engine the one above.
-constexpr int kGruChunks = 32, kGruChannels = 32;
+// eight channels are one 32-byte sector of a row: narrow blocks, so that one sequence already gives width / 8 of them
+constexpr int kGruChunks = 128, kGruChannels = 8;
 
 template <typename TO, typename TW>
 __global__ void __launch_bounds__(kGruChunks * kGruChannels)
@@ -328,7 +329,7 @@ mingru_scan_chunked_kernel(const float* __restrict__ p, int p_stride, const TW* 
 // out[t,c] = silu(sum_j w[c,j] * in(t - (taps-1) + j, c) + b[c]); in(.) is column in_col + c of the
 // projection rows of this step, or, before the step's first row of the sequence, the kept inputs
 // (`state`: [taps-1, channels] floats per slot, oldest first; zeros before the sequence's start).
-template <typename TW, typename TB>
+template <typename TW, typename TB, int VEC>
 __global__ void __launch_bounds__(256)
 causal_conv_silu_kernel(const float* __restrict__ proj, int proj_stride, int in_col, const TW* __restrict__ w,
                         const TB* __restrict__ b, int taps, int channels, const int* __restrict__ tok_seq,
@@ -340,15 +341,20 @@ causal_conv_silu_kernel(const float* __restrict__ proj, int proj_stride, int in_
     const int s = tok_seq[t];
     const int t0 = seq_start[s];
     const float* kept = state + (size_t)seq_slot[s] * state_stride;
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
-        float acc = to_float(b[c]);
+    MDMA_ROW_LOOP(c, channels, VEC) {
+        float acc[VEC];
+        RowVec<VEC, TB>::load(b + c, acc);
         for (int j = 0; j < taps; ++j) {
             const int src = t - (taps - 1) + j;            // a row of this step, or before it
-            const float v = src >= t0 ? proj[(size_t)src * proj_stride + in_col + c]
-                                      : kept[(size_t)(taps - 1 + (src - t0)) * channels + c];
-            acc = fmaf(to_float(w[(size_t)c * taps + j]), v, acc);
+            float v[VEC];
+            RowVec<VEC, float>::load(src >= t0 ? proj + (size_t)src * proj_stride + in_col + c
+                                               : kept + (size_t)(taps - 1 + (src - t0)) * channels + c, v);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = fmaf(to_float(w[(size_t)(c + i) * taps + j]), v[i], acc[i]);
         }
-        out[(size_t)t * channels + c] = silu_f(acc);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = silu_f(acc[i]);
+        RowVec<VEC, float>::store(out + (size_t)t * channels + c, acc);
     }
 }
 
@@ -738,10 +744,18 @@ int mdma_causal_conv_silu(const float* proj, int proj_stride, int in_col, const 
                  "causal_conv: bad sizes");
     MDMA_REQUIRE(n_seqs <= 65535, "causal_conv: too many sequences (%d)", n_seqs);
     if (n_rows == 0) return 0;
-    MDMA_DISPATCH_2(w_dtype, TW, b_dtype, TB,
-        launch_chained(causal_conv_silu_kernel<TW, TB>, dim3(n_rows, column_parts(channels)), dim3(256), 0, stream, proj, proj_stride, in_col,
-                       (const TW*)w, (const TB*)b, taps, channels, tok_seq, seq_start, seq_slot, (const float*)state,
-                       state_stride, out));
+    if (channels % 4 == 0 && in_col % 4 == 0 && proj_stride % 4 == 0 && state_stride % 4 == 0 &&
+        (((uintptr_t)proj | (uintptr_t)state | (uintptr_t)out) & 15) == 0) {
+        MDMA_DISPATCH_2(w_dtype, TW, b_dtype, TB,
+            launch_chained(causal_conv_silu_kernel<TW, TB, 4>, dim3(n_rows, column_parts(channels / 4)), dim3(256), 0, stream, proj,
+                           proj_stride, in_col, (const TW*)w, (const TB*)b, taps, channels, tok_seq, seq_start, seq_slot,
+                           (const float*)state, state_stride, out));
+    } else {
+        MDMA_DISPATCH_2(w_dtype, TW, b_dtype, TB,
+            launch_chained(causal_conv_silu_kernel<TW, TB, 1>, dim3(n_rows, column_parts(channels)), dim3(256), 0, stream, proj,
+                           proj_stride, in_col, (const TW*)w, (const TB*)b, taps, channels, tok_seq, seq_start, seq_slot,
+                           (const float*)state, state_stride, out));
+    }
     MDMA_LAUNCH_OK("causal_conv_silu");
     if (taps > 1) {
         launch_chained(conv_keep_kernel, dim3((channels + 255) / 256, n_seqs), dim3(256), 0, stream, proj, proj_stride,
