@@ -173,6 +173,10 @@ def compare(args) -> int:
         for name, ts in eng.model.expected_tensors().items():
             if len(ts.shape) == 2 and "embed" not in name:
                 matrix_bytes += 2 * ts.shape[0] * ts.shape[1]
+        # what a decode step moves besides the matrices: every live sequence's fixed-size state is read and written,
+        # and its cached rows (keys and values, or latents) are read
+        state_per_seq = eng.cache.state_bytes / eng.cache.max_slots
+        cache_per_token = sum(g.bytes for g in eng.cache.groups) / (eng.cache.n_pages * eng.page_size)
         times = []
         for i in range(warmup + 5):
             s = eng.acquire()
@@ -206,17 +210,18 @@ def compare(args) -> int:
         torch.cuda.synchronize()
         ms_d = e0.elapsed_time(e1) / steps
         launches = sess.launches_per_step
+        decode_bytes = matrix_bytes + batch * (2 * state_per_seq + (prompt + warmup + steps / 2) * cache_per_token)
         eng.check_status()
         del sess, eng
         gc.collect()
         torch.cuda.empty_cache()
-        # the matrices are read once per decode step and used twice per token and parameter in prefill; the cache
-        # and the state are left out of both counts (at these sizes a few per cent), so the shares are lower bounds
-        return {"matrix_gb": round(matrix_bytes / 1e9, 3),
+        # prefill: two operations per token and matrix element (attention and the scans are not counted, so the
+        # share is a lower bound); decode: the matrices once, every sequence's state twice, its cached rows once
+        return {"matrix_gb": round(matrix_bytes / 1e9, 3), "decode_gb_per_step": round(decode_bytes / 1e9, 3),
                 "prefill_tokens_per_s": round(T * 1000.0 / ms_p, 1), "prefill_ms": round(ms_p, 3),
                 "prefill_frac_of_bf16_peak": round(T * matrix_bytes / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4),
                 "decode_tokens_per_s": round(batch * 1000.0 / ms_d, 1), "decode_ms_per_step": round(ms_d, 4),
-                "decode_frac_of_hbm_peak": round(matrix_bytes / (ms_d * 1e-3) / 1e9 / hbm_gbs, 4),
+                "decode_frac_of_hbm_peak": round(decode_bytes / (ms_d * 1e-3) / 1e9 / hbm_gbs, 4),
                 "launches_per_decode_step": launches}
 
     clock = ClockSampler()

@@ -23,10 +23,10 @@ from .linear import Linear
 
 class HeadwiseLinear:
     """out[:, h*N:(h+1)*N] = a[:, h*K:(h+1)*K] @ w[h].T for every head h; w is [heads, N, K].  Steps of
-    many tokens run head by head on the tensor cores when the shapes allow, others as one launch on
-    the CUDA cores."""
+    many tokens (256 or more) run head by head on the tensor cores when the shapes allow, others as one
+    launch on the CUDA cores."""
 
-    TENSOR_TOKENS = 64
+    TENSOR_TOKENS = 256       # below this a launch per head costs more than the CUDA-core launch for all heads
 
     def __init__(self, w: torch.Tensor, rt):
         self.w, self.rt = w, rt
