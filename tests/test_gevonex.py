@@ -14,11 +14,15 @@ import plain_gevonex as pg
 from gevonex_tiny import CFG_A, CFG_B, CFG_C, CFG_D, CFG_E, make_model, make_tensors
 
 CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
-# float32: absolute, against the float64 statement.  bfloat16: absolute, and a row's root-mean-square error as a
-# share of the row's own deviation.  The largest seen on a B200 over all tests of this file: 6e-6 in float32;
-# 0.065 and 1.9 % in bfloat16 (GEVONEX_TEST_REPORT=1 prints them).
-TOL = {"float32": 5e-5, "bfloat16": 0.2}
-TOL_ROW_BF16 = 0.06
+# float32: absolute, against the float64 statement.  bfloat16: the largest error as a share of the deviation of the
+# reference logits it is compared with, and a row's root-mean-square error as a share of the row's own deviation.
+# The largest seen on a B200 (GEVONEX_TEST_REPORT=1 prints them) stand beside each.
+TOL_F32 = 5e-5                      # seen: 1.4e-5
+TOL_BF16, TOL_ROW_BF16 = 0.12, 0.06           # the five configurations of gevonex_tiny: seen 0.04 and 1.9 %
+# Drawn configurations can have norm parts of two elements, decays of e^-4.5 a unit step and recurrent layers a few
+# channels wide: there the rounding of a Mamba-2 layer's bfloat16 input alone moves the residual stream by 4 % (the
+# CUDA-core and the tensor-core kernels give the same 4 %; float32 on the same configurations stays within 1.4e-5).
+TOL_BF16_DRAWN, TOL_ROW_BF16_DRAWN = 0.4, 0.15  # seen 0.18 and 7.1 %
 
 
 def ids_of(cfg, n, seed):
@@ -29,17 +33,24 @@ def ids_of(cfg, n, seed):
 _largest = {}        # the largest errors seen, printed at exit when GEVONEX_TEST_REPORT is set
 
 
-def close(got, ref, dtype, what=""):
+def close(got, ref, dtype, what="", drawn=False):
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
     assert np.isfinite(got).all(), f"{what}: logits that are not finite"
     err = np.abs(got - ref)
-    _largest[dtype] = max(_largest.get(dtype, 0.0), float(err.max()))
-    assert err.max() < TOL[dtype], f"{what}: {err.max()}"
-    if dtype == "bfloat16" and ref.ndim == 2:
+    if dtype == "float32":
+        _largest[dtype] = max(_largest.get(dtype, 0.0), float(err.max()))
+        assert err.max() < TOL_F32, f"{what}: {err.max()}"
+        return
+    tol, tol_row = (TOL_BF16_DRAWN, TOL_ROW_BF16_DRAWN) if drawn else (TOL_BF16, TOL_ROW_BF16)
+    key = "drawn " if drawn else ""
+    share = float(err.max()) / max(float(ref.std()), 0.25)
+    _largest[key + dtype] = max(_largest.get(key + dtype, 0.0), share)
+    assert share < tol, f"{what}: {err.max()} is {share} of the logits' deviation"
+    if ref.ndim == 2:
         rel = np.sqrt((err ** 2).mean(axis=-1)) / ref.std(axis=-1)
-        _largest["row"] = max(_largest.get("row", 0.0), float(rel.max()))
-        assert rel.max() < TOL_ROW_BF16, f"{what}: row error {rel.max()} of the row's deviation"
+        _largest[key + "row"] = max(_largest.get(key + "row", 0.0), float(rel.max()))
+        assert rel.max() < tol_row, f"{what}: row error {rel.max()} of the row's deviation"
 
 
 if os.environ.get("GEVONEX_TEST_REPORT"):
@@ -689,3 +700,64 @@ def test_trace_replay_and_command_line(tmp_path):
     from mdma_b200.cli import main
     assert main(["run", d, " ".join(map(str, a[:5])), "--max-tokens", "4", "--dtype", "float32", "--max-context", "64"]) == 0
     assert main(["plan", d, "--ctx", "64"]) == 0
+
+
+def random_config(seed):
+    """A configuration drawn from plausible sizes: every mixer kind in any order, sizes that are and are not
+    multiples of 8 and 16, one to twenty heads, convolutions of one to eight taps, loops anywhere or nowhere."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([32, 40, 48, 64, 96, 128, 160, 192, 256])
+
+    def mixer(kind):
+        if kind == "mingru":
+            return {"width": r.choice([width, 2 * width, 24, 56])}
+        if kind == "mamba2":
+            heads = r.choice([1, 2, 3, 4, 6, 8])
+            vdim = r.choice([4, 8, 16, 24, 32, 48, 64])
+            groups = r.choice([g for g in (1, 2, 3, 4, 6, 8) if heads % g == 0])
+            norm_groups = r.choice([g for g in (1, 2, 4, heads) if (heads * vdim) % g == 0])
+            return {"heads": heads, "vdim": vdim, "state": r.choice([4, 8, 16, 24, 32, 48, 64, 128]), "groups": groups,
+                    "norm_groups": norm_groups, "conv": r.choice([1, 2, 3, 4, 5, 8])}
+        return {"heads": r.choice([1, 2, 3, 4, 8, 12, 16, 20]), "dim": r.choice([8, 16, 32, 48, 64]),
+                "vdim": r.choice([8, 16, 32, 64]), "kv_rank": r.choice([8, 16, 32, 40, 64, 96, 128, 144, 256]),
+                "scale": round(r.uniform(0.05, 0.4), 3)}
+    n = r.randint(2, 5)
+    kinds = [r.choice(["mingru", "mamba2", "latent_attention"]) for _ in range(n)]
+    layers = [{"type": k, "mixer": mixer(k),
+               "mlp": None if r.random() < 0.25 else {"kind": "dense", "ff": r.choice([width // 2, width, 2 * width, 3 * width + 8, 100])}}
+              for k in kinds]
+    cfg = {"architecture": "Gevonex", "vocab": r.randint(40, 500), "width": width, "norm": {"eps": r.choice([1e-5, 1e-6])},
+           "logit_softcap": r.choice([None, round(r.uniform(5, 50), 1)]), "layers": layers}
+    if r.random() < 0.7:
+        start = r.randint(0, n - 1)
+        cfg["loop"] = {"start": start, "stop": r.randint(start + 1, n), "times": r.randint(1, 3)}
+    return cfg
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations(seed):
+    """Ten drawn configurations in both engines: two unequal prompts in one step, six tokens decoded, against
+    the plain statement; pages of 16 or 64 rows."""
+    import random
+    from mdma_b200.engine import Engine, StepEntry
+    cfg = random_config(seed)
+    r = random.Random(1000 + seed)
+    lengths = [r.randint(30, 140), r.randint(1, 40)]
+    seqs = [ids_of(cfg, n + 6, 90 + seed + i) for i, n in enumerate(lengths)]
+    for dtype, store in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        d, W = make_model(cfg, 200 + seed, store)
+        refs = [pg.forward(cfg, W, s).numpy() for s in seqs]
+        eng = Engine(d, dtype=dtype, max_batch=2, max_context=192, logit_rows=192, page_size=r.choice([16, 64]))
+        slots = [eng.acquire(), eng.acquire()]
+        eng.cache.poison_unused()
+        out = eng.step([StepEntry(sl, s[:n], list(range(n))) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
+        close(out[:lengths[0]], refs[0][:lengths[0]], dtype, f"{cfg}: first prompt", drawn=True)
+        close(out[lengths[0]:], refs[1][:lengths[1]], dtype, f"{cfg}: second prompt", drawn=True)
+        for p in range(6):
+            eng.cache.poison_unused()
+            out = eng.step([StepEntry(sl, [s[n + p]], [0]) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
+            close(out, np.stack([refs[0][lengths[0] + p], refs[1][lengths[1] + p]]), dtype, f"{cfg}: decoded {p}", drawn=True)
+        eng.check_status()
+        del eng
