@@ -403,7 +403,18 @@ enum ScanPass : int { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 
 // NPT: the lanes that share a value column, when known at compile time (the common state sizes: loops unroll and
 // the index arithmetic folds), or 0: the run-time value `np_lanes` is used.
-template <int NPER, int VPT, int NPT, typename TW, int PASS>
+// TS: the type of the state, of the step sizes and decays and of the sums over the state: float, or double in the
+// exact engine (a decay is a product of up to thousands of factors below one, each rounded; in float that chain of
+// roundings, not the matrix products, is what a long sequence's result differs by from the exact one).  A double
+// state occupies two of the state row's floats per element.
+template <typename TS> __device__ __forceinline__ TS exp_t(TS v);
+template <> __device__ __forceinline__ float exp_t<float>(float v) { return expf(v); }
+template <> __device__ __forceinline__ double exp_t<double>(double v) { return exp(v); }
+template <typename TS> __device__ __forceinline__ TS softplus_t(TS v);
+template <> __device__ __forceinline__ float softplus_t<float>(float v) { return softplus_f(v); }
+template <> __device__ __forceinline__ double softplus_t<double>(double v) { return v > 40.0 ? v : log1p(exp(v)); }
+
+template <int NPER, int VPT, int NPT, typename TW, int PASS, typename TS = float>
 __global__ void __launch_bounds__(128)
 mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float* __restrict__ proj, int proj_stride,
                    int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log, const TW* __restrict__ D,
@@ -418,11 +429,11 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
     // VB = (threads / NP) * VPT columns
     const int VB = blockDim.x / NP * VPT;
     const int Npad = NP * NPER;
-    float* sB = sm;
+    TS* sdt = reinterpret_cast<TS*>(sm);                          // first: doubles want 8-byte alignment
+    TS* sa = sdt + kScanRows;
+    float* sB = reinterpret_cast<float*>(sa + kScanRows);
     float* sC = sB + kScanRows * Npad;
     float* sx = sC + kScanRows * Npad;
-    float* sdt = sx + kScanRows * VB;
-    float* sa = sdt + kScanRows;
     const int s = PASS == kScanWhole ? blockIdx.x : blockIdx.x / max_chunks;
     const int run = PASS == kScanWhole ? 0 : blockIdx.x % max_chunks;
     const int h = blockIdx.y, v0 = blockIdx.z * VB;
@@ -439,21 +450,23 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
     const int g = h / (heads / G);
     const int np = threadIdx.x % NP, vl = (threadIdx.x / NP) * VPT;       // first of this thread's columns, within the block
     const int inner = heads * vdim;
-    float* Sg = state + (size_t)seq_slot[s] * state_stride + (size_t)h * N * vdim;
-    float* Sc = PASS == kScanWhole ? nullptr : chunk_state + (size_t)blockIdx.x * state_floats + (size_t)h * N * vdim;
-    const float* Sfrom = PASS == kScanWhole ? Sg : Sc;
-    float S[VPT][NPER];
+    TS* Sg = reinterpret_cast<TS*>(state + (size_t)seq_slot[s] * state_stride) + (size_t)h * N * vdim;
+    TS* Sc = PASS == kScanWhole ? nullptr
+                                : reinterpret_cast<TS*>(chunk_state) + (size_t)blockIdx.x * state_floats + (size_t)h * N * vdim;
+    const TS* Sfrom = PASS == kScanWhole ? Sg : Sc;
+    TS S[VPT][NPER];
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int v = v0 + vl + j;
 #pragma unroll
         for (int i = 0; i < NPER; ++i) {
             const int n = np * NPER + i;
-            S[j][i] = (PASS != kScanLocal && v < vdim && n < N) ? Sfrom[(size_t)v * N + n] : 0.f;
+            S[j][i] = (PASS != kScanLocal && v < vdim && n < N) ? Sfrom[(size_t)v * N + n] : TS(0);
         }
     }
-    float dt_sum = 0.f;
-    const float rate = expf(to_float(A_log[h])), Dh = to_float(D[h]), bias = to_float(dt_bias[h]);
+    TS dt_sum = 0;
+    const TS rate = exp_t<TS>((TS)to_float(A_log[h])), bias = (TS)to_float(dt_bias[h]);
+    const float Dh = to_float(D[h]);
     for (int t0 = t_begin; t0 < t_end; t0 += kScanRows) {
         const int nt = min(kScanRows, t_end - t0);
         __syncthreads();
@@ -468,15 +481,15 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
             sx[i] = (v0 + vv < vdim) ? conv[(size_t)(t0 + tt) * conv_stride + h * vdim + v0 + vv] : 0.f;
         }
         for (int i = threadIdx.x; i < nt; i += blockDim.x) {
-            const float d = softplus_f(proj[(size_t)(t0 + i) * proj_stride + dt_col + h] + bias);
+            const TS d = softplus_t<TS>((TS)proj[(size_t)(t0 + i) * proj_stride + dt_col + h] + bias);
             sdt[i] = d;
-            sa[i] = expf(-rate * d);
+            sa[i] = exp_t<TS>(-rate * d);
         }
         __syncthreads();
         if (PASS == kScanLocal && threadIdx.x == 0)
             for (int tt = 0; tt < nt; ++tt) dt_sum += sdt[tt];
         for (int tt = 0; tt < nt; ++tt) {
-            const float a = sa[tt], dt = sdt[tt];
+            const TS a = sa[tt], dt = sdt[tt];
             // a thread's NPER entries of B and of C lie side by side: 16-byte shared-memory loads
             float Bt[NPER], Ct[NPER];
 #pragma unroll
@@ -488,16 +501,17 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
                     Ct[i] = c4.x; Ct[i + 1] = c4.y; Ct[i + 2] = c4.z; Ct[i + 3] = c4.w;
                 }
             }
-            float acc[VPT], xv[VPT];
+            TS acc[VPT];
+            float xv[VPT];
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 xv[j] = sx[tt * VB + vl + j];
-                const float dtx = dt * xv[j];
-                acc[j] = 0.f;
+                const TS dtx = dt * (TS)xv[j];
+                acc[j] = 0;
 #pragma unroll
                 for (int i = 0; i < NPER; ++i) {
-                    S[j][i] = fmaf(a, S[j][i], dtx * Bt[i]);
-                    if (PASS != kScanLocal) acc[j] = fmaf(S[j][i], Ct[i], acc[j]);
+                    S[j][i] = a * S[j][i] + dtx * (TS)Bt[i];              // one fused multiply-add and a multiply
+                    if (PASS != kScanLocal) acc[j] += S[j][i] * (TS)Ct[i];
                 }
             }
             if (PASS != kScanLocal) {
@@ -506,12 +520,12 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
 #pragma unroll
                     for (int o = NP >> 1; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
                     const int v = v0 + vl + j;
-                    if (np == 0 && v < vdim) y[(size_t)(t0 + tt) * inner + h * vdim + v] = acc[j] + Dh * xv[j];
+                    if (np == 0 && v < vdim) y[(size_t)(t0 + tt) * inner + h * vdim + v] = (float)(acc[j] + (TS)Dh * (TS)xv[j]);
                 }
             }
         }
     }
-    float* Sto = PASS == kScanLocal ? Sc : (last_run ? Sg : nullptr);
+    TS* Sto = PASS == kScanLocal ? Sc : (last_run ? Sg : nullptr);
     if (Sto != nullptr) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -524,7 +538,7 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
         }
     }
     if (PASS == kScanLocal && threadIdx.x == 0 && blockIdx.z == 0)
-        chunk_decay[(size_t)blockIdx.x * heads + h] = expf(-rate * dt_sum);
+        chunk_decay[(size_t)blockIdx.x * heads + h] = (float)exp_t<TS>(-rate * dt_sum);
 }
 
 // The runs' starting states, in order: start[0] = the sequence's state, start[r+1] = decay[r] * start[r] + local[r].
@@ -771,10 +785,12 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
                      const void* dt_bias, const void* A_log, const void* D, int w_dtype, const int* seq_start,
                      const int* seq_slot, float* state, long state_stride, float* y, int n_seqs, int heads, int vdim,
                      int N, int G, int chunk_rows, int max_chunks, float* scratch, long scratch_floats,
-                     cudaStream_t stream) {
+                     int wide_state, cudaStream_t stream) {
     MDMA_REQUIRE(heads > 0 && vdim > 0 && N > 0 && G > 0 && heads % G == 0, "mamba2_scan: bad geometry");
     MDMA_REQUIRE(N <= 256, "mamba2_scan: state size %d is beyond the kernel's 256", N);
-    MDMA_REQUIRE(state_stride >= (long)heads * N * vdim, "mamba2_scan: the state rows are too short");
+    MDMA_REQUIRE(state_stride >= (long)(wide_state ? 2 : 1) * heads * N * vdim, "mamba2_scan: the state rows are too short");
+    MDMA_REQUIRE(!wide_state || (chunk_rows <= 0 && state_stride % 2 == 0 && ((uintptr_t)state & 7) == 0),
+                 "mamba2_scan: a double state goes with the row-by-row walk and rows that start on 8-byte boundaries");
     MDMA_REQUIRE(n_seqs <= 65535 * 1 && heads <= 65535, "mamba2_scan: too many sequences or heads");
     if (n_seqs == 0) return 0;
     const int nper = 8;
@@ -782,7 +798,8 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     while (np * nper < N) np <<= 1;           // lanes per value column: a power of two, at most 32
     const int vpt = vdim >= 32 ? 4 : 1;       // value columns per thread: B and C are fetched once for all of a block's
     const int vb = 128 / np * vpt;
-    const size_t smem = sizeof(float) * (size_t)(2 * kScanRows * np * nper + kScanRows * vb + 2 * kScanRows);
+    const size_t smem = sizeof(float) * (size_t)(2 * kScanRows * np * nper + kScanRows * vb) +
+                        (wide_state ? sizeof(double) : sizeof(float)) * 2 * kScanRows;
     dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb);
     MDMA_REQUIRE(grid.z <= 65535, "mamba2_scan: value size %d is too large", vdim);
     float* chunk_state = nullptr;
@@ -818,6 +835,22 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
         MDMA_LAUNCH_OK("mamba2_chunk_starts");
         if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanFrom, "mamba2_scan (runs from their starts)"); }
         else { MDMA_SCAN_LAUNCH(1, kScanFrom, "mamba2_scan (runs from their starts)"); }
+        return 0;
+    }
+    if (wide_state) {
+        // the exact engine: state, step sizes, decays and the sums over the state in double
+        if (vpt == 4) {
+            MDMA_DISPATCH_DTYPE(w_dtype, TW,
+                launch_chained(mamba2_scan_kernel<8, 4, 0, TW, kScanWhole, double>, grid, dim3(128), smem, stream, conv, conv_stride,
+                               proj, proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,
+                               state, state_stride, y, heads, vdim, N, G, np, 0, 1, (float*)nullptr, (float*)nullptr));
+        } else {
+            MDMA_DISPATCH_DTYPE(w_dtype, TW,
+                launch_chained(mamba2_scan_kernel<8, 1, 0, TW, kScanWhole, double>, grid, dim3(128), smem, stream, conv, conv_stride,
+                               proj, proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot,
+                               state, state_stride, y, heads, vdim, N, G, np, 0, 1, (float*)nullptr, (float*)nullptr));
+        }
+        MDMA_LAUNCH_OK("mamba2_scan (double state)");
         return 0;
     }
     if (vpt == 4) { MDMA_SCAN_LAUNCH(4, kScanWhole, "mamba2_scan"); }

@@ -139,6 +139,10 @@ def plan_only(model_dir: str, dtype="bfloat16", max_batch: int = 1, max_context:
     arch, config = load_config(model_dir)
     spec = arch.describe(config)
     model = DecoderModel(spec)
+    for part in model.all_parts():          # parts may size their state by the engine's dtype
+        check = getattr(part, "check_limits", None)
+        if check is not None:
+            check(Runtime(_DTYPES[dtype], torch.device("meta")))
     ctx = int(max_context or spec.max_positions)
     max_tokens = max_batch * (-(-ctx // page_size)) * page_size
     try:

@@ -380,11 +380,14 @@ def causal_conv_silu(proj, in_col: int, w, b, taps: int, channels: int, tok_seq,
 
 
 def mamba2_scan(conv, proj, dt_col: int, dt_bias, a_log, d, seq_start, seq_slot, state, y, n_seqs: int, heads: int,
-                vdim: int, n_state: int, groups: int, chunk_rows: int = 0, max_chunks: int = 1, scratch=None) -> None:
+                vdim: int, n_state: int, groups: int, chunk_rows: int = 0, max_chunks: int = 1, scratch=None,
+                wide_state: bool = False) -> None:
     """The selective scan over each sequence's rows; `conv` rows are [x | B | C] after the convolution,
     `proj` holds the raw step sizes at columns dt_col + head; state [slots, heads * n_state * vdim] float.
     `chunk_rows` > 0: sequences are walked as runs of that many rows side by side (`max_chunks`: the most runs
-    of a sequence; `scratch`: n_seqs * max_chunks * (state size + heads) floats); equal up to rounding."""
+    of a sequence; `scratch`: n_seqs * max_chunks * (state size + heads) floats); equal up to rounding.
+    `wide_state`: the state rows hold doubles (two floats an element), and step sizes, decays and the sums over
+    the state are computed in double: the exact engine's walk."""
     _need_cuda(scratch)
     assert chunk_rows == 0 or (scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous())
     _need_cuda(conv, proj, dt_bias, a_log, d, seq_start, seq_slot, state, y)
@@ -394,7 +397,7 @@ def mamba2_scan(conv, proj, dt_col: int, dt_bias, a_log, d, seq_start, seq_slot,
     _call("core", "mdma_mamba2_scan", _ptr(conv), _i(conv.stride(0)), _ptr(proj), _i(proj.stride(0)), _i(dt_col),
           _ptr(dt_bias), _ptr(a_log), _ptr(d), _i(_same_dtype(dt_bias, a_log, d)), _ptr(seq_start), _ptr(seq_slot),
           sp, ss, _ptr(y), _i(n_seqs), _i(heads), _i(vdim), _i(n_state), _i(groups), _i(chunk_rows), _i(max_chunks),
-          _ptr(scratch), ctypes.c_long(scratch.numel() if scratch is not None else 0), _stream(),
+          _ptr(scratch), ctypes.c_long(scratch.numel() if scratch is not None else 0), _i(int(wide_state)), _stream(),
           launches=3 if chunk_rows > 0 else 1)
 
 

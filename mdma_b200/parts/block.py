@@ -55,8 +55,8 @@ class ShiftGatedBlock:
 
     The gates read h as the norm hands it out, before the shift; only the mixer reads shifted rows.
     Parts beyond a layer's four come from `LayerSpec.extras`: "shift" (token_shift), "mixer_gate" and
-    "ffn_gate" (residual_gate).  The run's state rows hold the shift's last h first, then the mixer's
-    own state.  Mixers and feed-forwards that offer `produce` (store their result as float rows) are
+    "ffn_gate" (residual_gate).  The run's state rows hold the mixer's own state first (padded to a
+    multiple of four floats, so that both parts start on 16-byte boundaries), then the shift's last h.  Mixers and feed-forwards that offer `produce` (store their result as float rows) are
     used that way; others run into a zeroed buffer through their ordinary `forward`."""
 
     def __init__(self, spec: LayerSpec):
@@ -82,23 +82,27 @@ class ShiftGatedBlock:
 
     def state_need(self):
         from ..cache import StateNeed
+        # rows of a multiple of four floats: every row, and the mixer's part of it, starts on a 16-byte boundary
+        return StateNeed((-(-(self._mixer_floats() + self.shift.state_floats()) // 4) * 4,), torch.float32)
+
+    def _mixer_floats(self) -> int:
+        """Floats of the mixer's state, rounded up to a multiple of four."""
         inner = self.mixer.state_need()
-        own = self.shift.state_floats()
         if inner is None:
-            return StateNeed((own,), torch.float32)
+            return 0
         if inner.dtype != torch.float32:
             raise ValueError("the arrangement keeps its state in float rows; so must its mixer")
         n = 1
         for d in inner.shape:
             n *= int(d)
-        return StateNeed((own + n,), torch.float32)
+        return -(-n // 4) * 4
 
     def forward(self, ctx, x, view, owns_cache=True):
         import dataclasses
         n, W = ctx.n_tokens, self.width
-        own = self.shift.state_floats()
-        shift_state = view.state[:, :own]
-        mixer_view = dataclasses.replace(view, state=view.state[:, own:] if view.state.shape[1] > own else None)
+        mixer_floats = self._mixer_floats()
+        shift_state = view.state[:, mixer_floats:mixer_floats + self.shift.state_floats()]
+        mixer_view = dataclasses.replace(view, state=view.state[:, :mixer_floats] if mixer_floats else None)
         h, hs, g = ctx.buf("normed", W), ctx.buf("shifted", W), ctx.buf("gate", W)
         y = ctx.buf("sublayer", W, torch.float32)
         if hasattr(self.mixer_norm, "forward_shifted"):
