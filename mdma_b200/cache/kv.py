@@ -3,7 +3,8 @@
 A *site* is one run of a layer in the model's schedule that keeps keys and
 values.  Sites with the same need (heads, head size, window) form a *group*
 with storage of its own: a pool of pages `[sites, pages, page_size, kv_heads,
-head_dim]` for keys and one for values, a free list of pages and one page
+head_dim]` for keys and one for values (none for a need with `values=False`:
+one vector per token that serves as both), a free list of pages and one page
 table `[slots, max_pages]`.  A sequence holds a slot, and in every group the
 pages that cover its length; groups with a window give pages back once every
 key in them has left the window.  Slots and pages go back to the free lists

@@ -4,6 +4,8 @@ feed_forward(norm(x)), the residual stream x kept in float
 in front of the mixer and a learned gate on each sublayer's result."""
 from __future__ import annotations
 
+import dataclasses
+
 import torch
 
 from ..registry import AUXILIARIES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS
@@ -98,8 +100,7 @@ class ShiftGatedBlock:
         return -(-n // 4) * 4
 
     def forward(self, ctx, x, view, owns_cache=True):
-        import dataclasses
-        n, W = ctx.n_tokens, self.width
+        W = self.width
         mixer_floats = self._mixer_floats()
         shift_state = view.state[:, mixer_floats:mixer_floats + self.shift.state_floats()]
         mixer_view = dataclasses.replace(view, state=view.state[:, :mixer_floats] if mixer_floats else None)

@@ -11,6 +11,8 @@ size kv_rank that serves as key and as value, whatever the number of heads.
 """
 from __future__ import annotations
 
+import dataclasses
+
 import torch
 
 from .. import ops
@@ -142,7 +144,6 @@ class LatentAttention(Part):
         self.absorb.run(proj, q_lat, n)
         if self._fast_ok:
             # the latent rows serve as the one key head and as the one value head
-            import dataclasses
             from .. import ops_tensor
             ops_tensor.attention(ctx, q_lat, dataclasses.replace(view, v=view.k), o_lat, self.n_heads, 1, self.rank,
                                  self.window, self.scale, st=self.rt.tc, sink_log2=self.sink_log2)
