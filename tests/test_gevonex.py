@@ -761,3 +761,37 @@ def test_random_configurations(seed):
             close(out, np.stack([refs[0][lengths[0] + p], refs[1][lengths[1] + p]]), dtype, f"{cfg}: decoded {p}", drawn=True)
         eng.check_status()
         del eng
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_plan_is_what_is_held_and_generation_takes_nothing_more(dtype):
+    """The memory plan made from sizes alone (state rows included: doubles for Mamba-2 in the 32-bit engine) is what
+    the engine holds, category by category and by the allocator's count; generation, sampled or not, takes nothing more."""
+    import gc
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.step import plan_only
+    d, cfg, W = model_of("A", dtype)
+    gc.collect()
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    eng = Engine(d, dtype=dtype, max_batch=3, max_context=128)
+    held = eng.held_bytes()
+    assert eng.plan["total_bytes"] == held["total_bytes"] == sum(v for k, v in held.items() if k != "total_bytes")
+    for key, value in held.items():
+        assert eng.plan[key] == value, (key, eng.plan[key], value)
+    taken = torch.cuda.memory_allocated() - before
+    assert 0 <= taken - eng.plan["total_bytes"] < (2 << 20), (taken, eng.plan["total_bytes"])
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert plan_only(d, dtype=dtype, max_batch=3, max_context=128, sms=sms) == eng.plan
+    prompts = [ids_of(cfg, n, 80 + n) for n in (5, 40, 17)]
+    eng.generate(prompts, max_tokens=20)                    # warm: kernels loaded, graphs captured
+    eng.generate(prompts, max_tokens=20, temperature=0.7, seed=3)
+    torch.cuda.synchronize()
+    warm = torch.cuda.memory_allocated()
+    for seed2 in range(3):
+        outs = eng.generate(prompts, max_tokens=30, temperature=0.9, top_p=0.9, seed=seed2)
+        assert all(len(o.tokens) == 30 for o in outs)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == warm
+    eng.cache.check()
