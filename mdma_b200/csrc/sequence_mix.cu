@@ -407,6 +407,15 @@ enum ScanPass : int { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 // exact engine (a decay is a product of up to thousands of factors below one, each rounded; in float that chain of
 // roundings, not the matrix products, is what a long sequence's result differs by from the exact one).  A double
 // state occupies two of the state row's floats per element.
+// 4-byte copies from global to shared memory that do not hold the thread up (cp.async), in groups that are waited for.
+__device__ __forceinline__ void async_copy_4(float* dst_shared, const float* src_global) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_shared);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(d), "l"(src_global) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 template <typename TS> __device__ __forceinline__ TS exp_t(TS v);
 template <> __device__ __forceinline__ float exp_t<float>(float v) { return expf(v); }
 template <> __device__ __forceinline__ double exp_t<double>(double v) { return exp(v); }
@@ -429,14 +438,15 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
     // VB = (threads / NP) * VPT columns
     const int VB = blockDim.x / NP * VPT;
     const int Npad = NP * NPER;
+    // The rows are staged through two sets of buffers: while one set of 16 rows is walked, the next is on its way
+    // (cp.async), so that the walk never waits for global memory.
     TS* sdt = reinterpret_cast<TS*>(sm);                          // first: doubles want 8-byte alignment
     TS* sa = sdt + kScanRows;
-    float* sB = reinterpret_cast<float*>(sa + kScanRows);
-    float* sC = sB + kScanRows * Npad;
-    float* sx = sC + kScanRows * Npad;
+    float* stage0 = reinterpret_cast<float*>(sa + kScanRows);
     const int s = PASS == kScanWhole ? blockIdx.x : blockIdx.x / max_chunks;
     const int run = PASS == kScanWhole ? 0 : blockIdx.x % max_chunks;
     const int h = blockIdx.y, v0 = blockIdx.z * VB;
+    const int inner_cols = heads * vdim, g_col = (h / (heads / G)) * N;
     int t_begin = seq_start[s], t_end = seq_start[s + 1];
     bool last_run = true;
     if (PASS != kScanWhole) {
@@ -447,7 +457,6 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
         t_end = min(t_end, t_begin + chunk_rows);
     }
     const size_t state_floats = (size_t)heads * N * vdim;
-    const int g = h / (heads / G);
     const int np = threadIdx.x % NP, vl = (threadIdx.x / NP) * VPT;       // first of this thread's columns, within the block
     const int inner = heads * vdim;
     TS* Sg = reinterpret_cast<TS*>(state + (size_t)seq_slot[s] * state_stride) + (size_t)h * N * vdim;
@@ -467,21 +476,49 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
     TS dt_sum = 0;
     const TS rate = exp_t<TS>((TS)to_float(A_log[h])), bias = (TS)to_float(dt_bias[h]);
     const float Dh = to_float(D[h]);
-    for (int t0 = t_begin; t0 < t_end; t0 += kScanRows) {
-        const int nt = min(kScanRows, t_end - t0);
-        __syncthreads();
+    const int stage_floats = kScanRows * (2 * Npad + VB + 1);     // B, C, x and the raw step sizes of 16 rows
+    auto issue = [&](int t0, int nt, float* base) {
+        float* pB = base; float* pC = pB + kScanRows * Npad; float* px = pC + kScanRows * Npad; float* pr = px + kScanRows * VB;
         for (int i = threadIdx.x; i < nt * Npad; i += blockDim.x) {
             const int tt = i / Npad, n = i % Npad;
-            const float* row = conv + (size_t)(t0 + tt) * conv_stride + inner + g * N;
-            sB[i] = n < N ? row[n] : 0.f;
-            if (PASS != kScanLocal) sC[i] = n < N ? row[G * N + n] : 0.f;
+            if (n < N) {
+                const float* row = conv + (size_t)(t0 + tt) * conv_stride + inner_cols + g_col;
+                async_copy_4(pB + i, row + n);
+                if (PASS != kScanLocal) async_copy_4(pC + i, row + G * N + n);
+            }
         }
         for (int i = threadIdx.x; i < nt * VB; i += blockDim.x) {
             const int tt = i / VB, vv = i % VB;
-            sx[i] = (v0 + vv < vdim) ? conv[(size_t)(t0 + tt) * conv_stride + h * vdim + v0 + vv] : 0.f;
+            if (v0 + vv < vdim) async_copy_4(px + i, conv + (size_t)(t0 + tt) * conv_stride + h * vdim + v0 + vv);
         }
+        for (int i = threadIdx.x; i < nt; i += blockDim.x)
+            async_copy_4(pr + i, proj + (size_t)(t0 + i) * proj_stride + dt_col + h);
+        async_commit();
+    };
+    // entries that no copy writes (state rows beyond N, value columns beyond vdim), if there are any, are zero in both sets
+    if (Npad > N || v0 + VB > vdim) {
+        for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) stage0[i] = 0.f;
+        __syncthreads();
+    }
+    int set = 0;
+    if (t_begin < t_end) issue(t_begin, min(kScanRows, t_end - t_begin), stage0);
+    for (int t0 = t_begin; t0 < t_end; t0 += kScanRows, set ^= 1) {
+        const int nt = min(kScanRows, t_end - t0);
+        float* base = stage0 + set * stage_floats;
+        const float* sB = base;
+        const float* sC = sB + kScanRows * Npad;
+        const float* sx = sC + kScanRows * Npad;
+        const float* sraw = sx + kScanRows * VB;
+        // the other set was read in the round before (the barrier at this loop's end): fill it with the next rows
+        if (t0 + kScanRows < t_end) {
+            issue(t0 + kScanRows, min(kScanRows, t_end - t0 - kScanRows), stage0 + (set ^ 1) * stage_floats);
+            async_wait_but_one();
+        } else {
+            async_wait_all();
+        }
+        __syncthreads();                                   // this set's rows have landed, for every thread
         for (int i = threadIdx.x; i < nt; i += blockDim.x) {
-            const TS d = softplus_t<TS>((TS)proj[(size_t)(t0 + i) * proj_stride + dt_col + h] + bias);
+            const TS d = softplus_t<TS>((TS)sraw[i] + bias);
             sdt[i] = d;
             sa[i] = exp_t<TS>(-rate * d);
         }
@@ -524,6 +561,7 @@ mamba2_scan_kernel(const float* __restrict__ conv, int conv_stride, const float*
                 }
             }
         }
+        __syncthreads();                                   // everyone is done with this set and with sdt, sa
     }
     TS* Sto = PASS == kScanLocal ? Sc : (last_run ? Sg : nullptr);
     if (Sto != nullptr) {
@@ -798,7 +836,8 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     while (np * nper < N) np <<= 1;           // lanes per value column: a power of two, at most 32
     const int vpt = vdim >= 32 ? 4 : 1;       // value columns per thread: B and C are fetched once for all of a block's
     const int vb = 128 / np * vpt;
-    const size_t smem = sizeof(float) * (size_t)(2 * kScanRows * np * nper + kScanRows * vb) +
+    // two sets of staged rows (B, C, x, raw step sizes), then the step sizes and decays of the set being walked
+    const size_t smem = sizeof(float) * 2 * (size_t)(kScanRows * (2 * np * nper + vb + 1)) +
                         (wide_state ? sizeof(double) : sizeof(float)) * 2 * kScanRows;
     dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb);
     MDMA_REQUIRE(grid.z <= 65535, "mamba2_scan: value size %d is too large", vdim);
@@ -816,6 +855,10 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
         chunk_rows = 0; max_chunks = 1;
     }
 #define MDMA_SCAN_LAUNCH_NP(VPT_, NPT_, PASS_, what)                                                                   \
+    if (smem > 48 * 1024) {                                                                                            \
+        MDMA_DISPATCH_DTYPE(w_dtype, TW,                                                                               \
+            cudaFuncSetAttribute(mamba2_scan_kernel<8, VPT_, NPT_, TW, PASS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    }                                                                                                                  \
     MDMA_DISPATCH_DTYPE(w_dtype, TW,                                                                                   \
         launch_chained(mamba2_scan_kernel<8, VPT_, NPT_, TW, PASS_>, grid, dim3(128), smem, stream, conv, conv_stride,   \
                        proj, proj_stride, dt_col, (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, seq_start, seq_slot, \
@@ -839,6 +882,12 @@ int mdma_mamba2_scan(const float* conv, int conv_stride, const float* proj, int 
     }
     if (wide_state) {
         // the exact engine: state, step sizes, decays and the sums over the state in double
+        if (smem > 48 * 1024) {
+            MDMA_DISPATCH_DTYPE(w_dtype, TW,
+                cudaFuncSetAttribute(mamba2_scan_kernel<8, 4, 0, TW, kScanWhole, double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MDMA_DISPATCH_DTYPE(w_dtype, TW,
+                cudaFuncSetAttribute(mamba2_scan_kernel<8, 1, 0, TW, kScanWhole, double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        }
         if (vpt == 4) {
             MDMA_DISPATCH_DTYPE(w_dtype, TW,
                 launch_chained(mamba2_scan_kernel<8, 4, 0, TW, kScanWhole, double>, grid, dim3(128), smem, stream, conv, conv_stride,
