@@ -3,8 +3,9 @@
 A *site* is one run of a layer in the model's schedule that keeps keys and
 values.  Sites with the same need (heads, head size, window) form a *group*
 with storage of its own: a pool of pages `[sites, pages, page_size, kv_heads,
-head_dim]` for keys and one for values (none for a need with `values=False`:
-one vector per token that serves as both), a free list of pages and one page
+head_dim]` for keys and one for values (of `v_dim` numbers a head where that
+differs from the keys'; none for a need with `values=False`: one vector per
+token that serves as both), a free list of pages and one page
 table `[slots, max_pages]`.  A sequence holds a slot, and in every group the
 pages that cover its length; groups with a window give pages back once every
 key in them has left the window.  Slots and pages go back to the free lists
@@ -34,6 +35,7 @@ class KVNeed:
     head_dim: int
     window: int = 0          # 0: every key is kept; n: only the last n keys are read
     values: bool = True      # False: one vector per token only (a latent that serves as key and value)
+    v_dim: int = 0           # size of a value head when it differs from the key's (0: the same)
 
 
 @dataclass(frozen=True)
@@ -65,10 +67,12 @@ class CacheGroup:
         self.seq_pages: dict[int, dict[int, int]] = {}      # slot -> {page index in sequence: page}
         self.dirty: set[int] = set()
         shape = (len(sites), n_pages, page_size, need.n_kv_heads, need.head_dim)
-        self.bytes = (2 if need.values else 1) * int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        v_shape = shape[:-1] + (need.v_dim or need.head_dim,)
+        self.bytes = ((int(np.prod(shape)) + (int(np.prod(v_shape)) if need.values else 0))
+                      * torch.empty((), dtype=dtype).element_size())
         # `alloc(shape, dtype)` hands out zeroed device memory, or None when only sizes are wanted
         self.k = alloc(shape, dtype)
-        self.v = alloc(shape, dtype) if need.values else None
+        self.v = alloc(v_shape, dtype) if need.values else None
         self.table_dev = alloc((n_slots, max_pages), torch.int32)
 
     def grow(self, slot: int, old_len: int, new_len: int) -> None:

@@ -10,7 +10,7 @@ namespace mdma {
 // x[t,:] = float(table[ids[t],:]).  The residual stream is float in both engines.
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                  float* __restrict__ out, int width, int vocab) {
+                                  float* __restrict__ out, int width, int vocab, float scale) {
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
@@ -21,7 +21,7 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
         return;
     }
     const T* row = table + (size_t)id * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) o[e] = to_float(row[e]);
+    for (int e = threadIdx.x; e < width; e += blockDim.x) o[e] = to_float(row[e]) * scale;
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -533,14 +533,20 @@ int mdma_advance_decode(const int* tokens, int* ids, int* tok_pos, int* seq_pos0
 
 const char* mdma_last_error() { return error_buffer(); }
 
-int mdma_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
-                    int n_tokens, int width, int vocab, cudaStream_t stream) {
+// out[t,:] = table[ids[t],:] * scale (the product in float; scale 1 leaves the table's values as they are)
+int mdma_embed_rows_scaled(const void* table, int table_dtype, const int* ids, float* out,
+                           int n_tokens, int width, int vocab, float scale, cudaStream_t stream) {
     MDMA_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes");
     if (n_tokens == 0) return 0;
     MDMA_DISPATCH_DTYPE(table_dtype, T,
-        launch_chained(embed_rows_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table, ids, out, width, vocab));
+        launch_chained(embed_rows_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table, ids, out, width, vocab, scale));
     MDMA_LAUNCH_OK("embed_rows");
     return 0;
+}
+
+int mdma_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                    int n_tokens, int width, int vocab, cudaStream_t stream) {
+    return mdma_embed_rows_scaled(table, table_dtype, ids, out, n_tokens, width, vocab, 1.0f, stream);
 }
 
 // partial/splits: optional K-split partial sums [splits, rows_total, width] to add into x first

@@ -165,5 +165,7 @@ extern "C" int mdma_gemm_simt_batched(const void* A, int a_dtype, int lda, long 
         return launch_gemm<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(kStore, A, lda, W, nullptr, out, ldo, M, N, K, e, stream, batch, batch_a, batch_w, batch_o);
     if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kF32)
         return launch_gemm<__nv_bfloat16, __nv_bfloat16, float>(kStore, A, lda, W, nullptr, out, ldo, M, N, K, e, stream, batch, batch_a, batch_w, batch_o);
+    if (a_dtype == kF32 && w_dtype == kBF16 && out_dtype == kF32)       // float rows through matrices kept in bfloat16 (a recurrence's gates)
+        return launch_gemm<float, __nv_bfloat16, float>(kStore, A, lda, W, nullptr, out, ldo, M, N, K, e, stream, batch, batch_a, batch_w, batch_o);
     return fail("gemm_simt_batched: unsupported dtypes a=%d w=%d out=%d", a_dtype, w_dtype, out_dtype);
 }

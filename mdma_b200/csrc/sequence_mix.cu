@@ -326,7 +326,7 @@ mingru_scan_chunked_kernel(const float* __restrict__ p, int p_stride, const TW* 
 }
 
 // ---------------------------------------------------------------- short causal convolution
-// out[t,c] = silu(sum_j w[c,j] * in(t - (taps-1) + j, c) + b[c]); in(.) is column in_col + c of the
+// out[t,c] = silu(sum_j w[c,j] * in(t - (taps-1) + j, c) + b[c]) (or the sum itself, `silu` = 0); in(.) is column in_col + c of the
 // projection rows of this step, or, before the step's first row of the sequence, the kept inputs
 // (`state`: [taps-1, channels] floats per slot, oldest first; zeros before the sequence's start).
 template <typename TW, typename TB, int VEC>
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(256)
 causal_conv_silu_kernel(const float* __restrict__ proj, int proj_stride, int in_col, const TW* __restrict__ w,
                         const TB* __restrict__ b, int taps, int channels, const int* __restrict__ tok_seq,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
-                        const float* __restrict__ state, long state_stride, float* __restrict__ out) {
+                        const float* __restrict__ state, long state_stride, float* __restrict__ out, int silu) {
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
@@ -352,8 +352,10 @@ causal_conv_silu_kernel(const float* __restrict__ proj, int proj_stride, int in_
 #pragma unroll
             for (int i = 0; i < VEC; ++i) acc[i] = fmaf(to_float(w[(size_t)(c + i) * taps + j]), v[i], acc[i]);
         }
+        if (silu) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] = silu_f(acc[i]);
+            for (int i = 0; i < VEC; ++i) acc[i] = silu_f(acc[i]);
+        }
         RowVec<VEC, float>::store(out + (size_t)t * channels + c, acc);
     }
 }
@@ -787,10 +789,11 @@ int mdma_mingru_scan(const float* p, int p_stride, const void* bz, const void* b
     return 0;
 }
 
-int mdma_causal_conv_silu(const float* proj, int proj_stride, int in_col, const void* w, int w_dtype, const void* b,
-                          int b_dtype, int taps, int channels, const int* tok_seq, const int* seq_start,
-                          const int* seq_slot, float* state, long state_stride, float* out, int n_rows, int n_seqs,
-                          cudaStream_t stream) {
+// `silu` = 0: the convolution's sum with its bias, no activation
+int mdma_causal_conv(const float* proj, int proj_stride, int in_col, const void* w, int w_dtype, const void* b,
+                     int b_dtype, int taps, int channels, const int* tok_seq, const int* seq_start,
+                     const int* seq_slot, float* state, long state_stride, float* out, int n_rows, int n_seqs,
+                     int silu, cudaStream_t stream) {
     MDMA_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal_conv: %d taps, the kernel takes 1..%d", taps, kMaxTaps);
     MDMA_REQUIRE(channels > 0 && proj_stride >= in_col + channels && state_stride >= (long)(taps - 1) * channels,
                  "causal_conv: bad sizes");
@@ -801,20 +804,28 @@ int mdma_causal_conv_silu(const float* proj, int proj_stride, int in_col, const 
         MDMA_DISPATCH_2(w_dtype, TW, b_dtype, TB,
             launch_chained(causal_conv_silu_kernel<TW, TB, 4>, dim3(n_rows, column_parts(channels / 4)), dim3(256), 0, stream, proj,
                            proj_stride, in_col, (const TW*)w, (const TB*)b, taps, channels, tok_seq, seq_start, seq_slot,
-                           (const float*)state, state_stride, out));
+                           (const float*)state, state_stride, out, silu));
     } else {
         MDMA_DISPATCH_2(w_dtype, TW, b_dtype, TB,
             launch_chained(causal_conv_silu_kernel<TW, TB, 1>, dim3(n_rows, column_parts(channels)), dim3(256), 0, stream, proj,
                            proj_stride, in_col, (const TW*)w, (const TB*)b, taps, channels, tok_seq, seq_start, seq_slot,
-                           (const float*)state, state_stride, out));
+                           (const float*)state, state_stride, out, silu));
     }
-    MDMA_LAUNCH_OK("causal_conv_silu");
+    MDMA_LAUNCH_OK("causal_conv");
     if (taps > 1) {
         launch_chained(conv_keep_kernel, dim3((channels + 255) / 256, n_seqs), dim3(256), 0, stream, proj, proj_stride,
                        in_col, taps, channels, seq_start, seq_slot, state, state_stride);
         MDMA_LAUNCH_OK("conv_keep");
     }
     return 0;
+}
+
+int mdma_causal_conv_silu(const float* proj, int proj_stride, int in_col, const void* w, int w_dtype, const void* b,
+                          int b_dtype, int taps, int channels, const int* tok_seq, const int* seq_start,
+                          const int* seq_slot, float* state, long state_stride, float* out, int n_rows, int n_seqs,
+                          cudaStream_t stream) {
+    return mdma_causal_conv(proj, proj_stride, in_col, w, w_dtype, b, b_dtype, taps, channels, tok_seq, seq_start, seq_slot,
+                            state, state_stride, out, n_rows, n_seqs, 1, stream);
 }
 
 // `chunk_rows` > 0: every sequence is walked as runs of that many rows side by side (at most `max_chunks` runs a

@@ -67,13 +67,14 @@ _i = ctypes.c_int
 _f = ctypes.c_float
 
 
-def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale, as float rows."""
     _need_cuda(table, ids, out)
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
     n = ids.numel()
     assert out.shape[0] >= n and out.shape[1] == table.shape[1] and out.is_contiguous()
-    _call("core", "mdma_embed_rows", _ptr(table), _i(dtype_code(table.dtype)), _ptr(ids), _ptr(out),
-          _i(n), _i(table.shape[1]), _i(table.shape[0]), _stream())
+    _call("core", "mdma_embed_rows_scaled", _ptr(table), _i(dtype_code(table.dtype)), _ptr(ids), _ptr(out),
+          _i(n), _i(table.shape[1]), _i(table.shape[0]), _f(scale), _stream())
 
 
 def fill_normal(out: torch.Tensor, key: int, table: torch.Tensor, std: float) -> None:
@@ -366,17 +367,17 @@ def mingru_scan(p, bz, bu, seq_start, seq_slot, state, out, n_seqs: int, width: 
 
 
 def causal_conv_silu(proj, in_col: int, w, b, taps: int, channels: int, tok_seq, seq_start, seq_slot, state, out,
-                     n_rows: int, n_seqs: int) -> None:
+                     n_rows: int, n_seqs: int, silu: bool = True) -> None:
     """out[t, c] = silu(bias + sum_j w[c, j] * input(t - taps + 1 + j, c)) over columns in_col.. of the float
     projection rows; inputs before the step come from `state` ([taps-1, channels] per slot), which is then
-    brought up to date."""
+    brought up to date.  `silu=False`: the sum itself, no activation."""
     _need_cuda(proj, w, b, tok_seq, seq_start, seq_slot, state, out)
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
     assert w.is_contiguous() and tuple(w.shape) == (channels, taps) and b.numel() == channels and out.shape[1] == channels
     sp, ss = _state(state)
-    _call("core", "mdma_causal_conv_silu", _ptr(proj), _i(proj.stride(0)), _i(in_col), _ptr(w), _i(dtype_code(w.dtype)),
+    _call("core", "mdma_causal_conv", _ptr(proj), _i(proj.stride(0)), _i(in_col), _ptr(w), _i(dtype_code(w.dtype)),
           _ptr(b), _i(dtype_code(b.dtype)), _i(taps), _i(channels), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot),
-          sp, ss, _ptr(out), _i(n_rows), _i(n_seqs), _stream(), launches=2 if taps > 1 else 1)
+          sp, ss, _ptr(out), _i(n_rows), _i(n_seqs), _i(int(silu)), _stream(), launches=2 if taps > 1 else 1)
 
 
 def mamba2_scan(conv, proj, dt_col: int, dt_bias, a_log, d, seq_start, seq_slot, state, y, n_seqs: int, heads: int,
@@ -444,3 +445,130 @@ def latent_attention(q, cache, sink, tok_seq, tok_pos, seq_slot, page_table, max
     _call("core", "mdma_latent_attention", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(cache), _ptr(sink),
           _i(dtype_code(sink.dtype)), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
           _i(page_size), _ptr(out), _i(n_tokens), _i(n_heads), _i(rank), _i(window), _f(scale), _stream())
+
+
+# ---- layer norm, loop re-entry by addition, row scale, the real-gated linear recurrence (csrc/rglru.cu) ---------
+def layernorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+              n_rows: Optional[int] = None) -> None:
+    """out[i] = (x[r] - mean) / sqrt(var + eps) * w, r = rows[i] or i; x is the float residual stream."""
+    _need_cuda(x, w, out, rows)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    width = x.shape[-1]
+    assert w.numel() == width and out.shape[-1] == width and w.is_contiguous()
+    n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert out.shape[0] >= n and (rows is None or rows.dtype == torch.int32)
+    _call("core", "mdma_layernorm", _ptr(x), _ptr(w), _i(dtype_code(w.dtype)), _ptr(rows), _ptr(out),
+          _i(dtype_code(out.dtype)), _i(n), _i(width), _f(eps), _stream())
+
+
+def loop_add(x: torch.Tensor, x0: Optional[torch.Tensor], step: torch.Tensor, n_rows: int) -> None:
+    """x[t] = (x[t] + x0[t]) + step (x0 None: only the vector is added); x, x0 float rows."""
+    _need_cuda(x, x0, step)
+    width = x.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and step.numel() == width and step.is_contiguous()
+    assert x0 is None or (x0.dtype == torch.float32 and x0.is_contiguous() and x0.shape[1] == width)
+    _call("core", "mdma_loop_add", _ptr(x), _ptr(x0), _ptr(step), _i(dtype_code(step.dtype)), _i(n_rows), _i(width), _stream())
+
+
+def scale_rows(v: torch.Tensor, s: torch.Tensor, n_rows: int) -> None:
+    """v[t, :] *= s[t] in place; s float."""
+    _need_cuda(v, s)
+    assert v.is_contiguous() and s.dtype == torch.float32 and s.is_contiguous() and s.numel() >= n_rows
+    _call("core", "mdma_scale_rows", _ptr(v), _i(dtype_code(v.dtype)), _ptr(s), _i(n_rows), _i(v.shape[1]), _stream())
+
+
+def rglru_scan(gates_r, gates_i, u, y, rb, ib, lam, decay: float, seq_start, seq_slot, state, out, n_seqs: int,
+               width: int, runs: bool = False) -> None:
+    """The real-gated linear recurrence over each sequence's rows: gates_r, gates_i, u [T, width] floats (the
+    gates' products before bias and sigmoid, the convolved branch), y float rows (the other branch before its
+    GELU; may be a view of wider rows), rb, ib, lam [width]; writes S * gelu(y) and keeps S in `state`.
+    `runs`: the side-by-side walk for steps of many rows per sequence (equal up to rounding)."""
+    _need_cuda(gates_r, gates_i, u, y, rb, ib, lam, seq_start, seq_slot, state, out)
+    for t in (gates_r, gates_i, u):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[1] == width
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and y.shape[1] == width
+    assert out.is_contiguous() and out.shape[1] == width
+    sp, ss = _state(state)
+    _call("core", "mdma_rglru_scan", _ptr(gates_r), _ptr(gates_i), _ptr(u), _ptr(y), _i(y.stride(0)), _ptr(rb), _ptr(ib),
+          _ptr(lam), _i(_same_dtype(rb, ib, lam)), _f(decay), _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out),
+          _i(dtype_code(out.dtype)), _i(n_seqs), _i(width), _i(int(runs)), _stream())
+
+
+# ---- attention with a penalty on distance (csrc/attention_distance.cu) -------------------------------------------
+def kv_store(proj, k_col: int, v_col: int, k_width: int, v_width: int, tok_seq, tok_pos, seq_slot, page_table,
+             max_pages: int, page_size: int, k_cache, v_cache, n_tokens: int) -> None:
+    """The k and v parts of the projection rows go to the tokens' cache rows (no position encoding)."""
+    _need_cuda(proj, tok_seq, tok_pos, seq_slot, page_table, k_cache, v_cache)
+    assert proj.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.dtype == proj.dtype == v_cache.dtype
+    _call("core", "mdma_kv_store", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(k_col), _i(v_col),
+          _i(k_width), _i(v_width), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
+          _i(page_size), _ptr(k_cache), _ptr(v_cache), _i(n_tokens), _stream())
+
+
+def attention_distance_tiled_fits(n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> bool:
+    lib = _build._loaded.get("core") or _build.load("core")
+    return bool(lib.mdma_attention_distance_tiled_fits(_i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim)))
+
+
+def attention_distance(q, k_cache, v_cache, ctx, page_table, max_pages: int, page_size: int, slopes, gate, out,
+                       n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int, scale: float,
+                       tiled: bool = False) -> None:
+    """Softmax attention with score (q.k) * scale - slopes[h] * distance over the paged cache; q: rows whose first
+    n_heads * dim columns are the queries; `gate` (rows of n_heads * v_dim, optional): the result is multiplied by
+    its sigmoid; out [T, n_heads * v_dim].  `tiled`: the kernel that stages keys and values per tile of query rows."""
+    _need_cuda(q, k_cache, v_cache, page_table, slopes, gate, out)
+    assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == k_cache.dtype == v_cache.dtype
+    assert out.shape[1] == n_heads * v_dim and out.shape[0] >= ctx.n_tokens
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == n_heads and slopes.is_contiguous())
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_heads * v_dim)
+    _call("core", "mdma_attention_distance", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(k_cache), _ptr(v_cache),
+          _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0),
+          _ptr(page_table), _i(max_pages), _i(page_size), _ptr(slopes), _ptr(gate),
+          _i(gate.stride(0) if gate is not None else 0), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs), _i(ctx.max_new),
+          _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _i(int(tiled)), _stream())
+
+
+# ---- routed feed-forward (csrc/routed_ffn.cu) -----------------------------------------------------------------------
+def route(h, router, correction, shared_gate, n_tokens: int, top: int, n_groups: int, keep_groups: int, chosen, weights,
+          shared_scale) -> None:
+    """Per token: softmax over the router's logits, choice among the best groups, `top` experts and their
+    normalised weights; with `shared_gate` [width] also sigmoid(shared_gate . h) into `shared_scale`."""
+    _need_cuda(h, router, correction, shared_gate, chosen, weights, shared_scale)
+    n_routed, width = router.shape
+    assert h.stride(1) == 1 and h.shape[1] == width and router.is_contiguous()
+    assert chosen.dtype == torch.int32 and weights.dtype == torch.float32 and chosen.is_contiguous() and weights.is_contiguous()
+    assert correction is None or (correction.numel() == n_routed and correction.is_contiguous())
+    assert shared_gate is None or (shared_gate.numel() == width and shared_gate.dtype == router.dtype and shared_gate.is_contiguous())
+    _call("core", "mdma_route", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(router), _i(dtype_code(router.dtype)),
+          _ptr(correction), _i(dtype_code(correction.dtype) if correction is not None else F32), _ptr(shared_gate),
+          _i(n_tokens), _i(width), _i(n_routed), _i(top), _i(n_groups), _i(keep_groups), _ptr(chosen), _ptr(weights),
+          _ptr(shared_scale), _stream())
+
+
+def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: int, top: int, ff: int, act, x,
+            sorted_scratch=None) -> None:
+    """x += sum over each token's chosen experts of weight * expert(h) (identity experts: weight * h).  gate_w, up_w
+    [experts * ff, width], down_w [experts * width, ff]; act [tokens * top, ff] scratch in h's dtype.
+    `sorted_scratch` = (first, order, y): the expert-by-expert kernels (steps of many tokens); else token by token."""
+    _need_cuda(h, gate_w, up_w, down_w, chosen, weights, act, x)
+    width = h.shape[1]
+    assert h.stride(1) == 1 and x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == width
+    assert act.is_contiguous() and act.dtype == h.dtype and act.shape[1] == ff
+    if n_experts:
+        assert gate_w.is_contiguous() and up_w.is_contiguous() and down_w.is_contiguous()
+        assert tuple(gate_w.shape) == (n_experts * ff, width) == tuple(up_w.shape) and tuple(down_w.shape) == (n_experts * width, ff)
+        assert gate_w.dtype == up_w.dtype == down_w.dtype
+    wd = dtype_code(gate_w.dtype) if n_experts else dtype_code(h.dtype)
+    if sorted_scratch is None:
+        _call("core", "mdma_experts_by_token", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(gate_w), _ptr(up_w),
+              _ptr(down_w), _i(wd), _ptr(chosen), _ptr(weights), _i(n_tokens), _i(n_experts), _i(top), _i(width), _i(ff),
+              _ptr(act), _ptr(x), _stream(), launches=2)
+        return
+    first, order, y = sorted_scratch
+    _need_cuda(first, order, y)
+    assert first.dtype == order.dtype == torch.int32 and first.numel() >= n_experts + 1 and order.numel() >= n_tokens * top
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.numel() >= n_tokens * top * width
+    _call("core", "mdma_experts_sorted", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(gate_w), _ptr(up_w),
+          _ptr(down_w), _i(wd), _ptr(chosen), _ptr(weights), _i(n_tokens), _i(n_experts), _i(top), _i(width), _i(ff),
+          _ptr(first), _ptr(order), _ptr(act), _ptr(y), _ptr(x), _stream(), launches=4)

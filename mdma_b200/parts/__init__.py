@@ -1,5 +1,6 @@
 """Parts a layer is put together from; importing this package registers them."""
-from . import attention, block, embedding, gating, latent_attention, mlp, norm, recurrent, rotary  # noqa: F401
+from . import (attention, block, distance_attention, embedding, gating, latent_attention, mlp, norm, recurrent,  # noqa: F401
+               rotary, routed_mlp)
 from .base import Part, Runtime
 from .linear import Linear
 

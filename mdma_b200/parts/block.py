@@ -1,7 +1,8 @@
 """How a layer's parts are arranged.  "prenorm": x += mixer(norm(x)); x +=
 feed_forward(norm(x)), the residual stream x kept in float
 (src/model/arch/llama.rs:181-231).  "shift_gated": the same with a token shift
-in front of the mixer and a learned gate on each sublayer's result."""
+in front of the mixer and a learned gate on each sublayer's result.  "parallel":
+one norm whose output both sublayers read, x += mixer(h) + feed_forward(h)."""
 from __future__ import annotations
 
 import dataclasses
@@ -133,3 +134,30 @@ class ShiftGatedBlock:
         if ctx.rt.gemm == "tensor":
             from .. import ops_tensor
             ops_tensor.flush_pending(y.device, ctx.rt.tc)
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock:
+    """One norm, two readers:  h = norm(x);  x += mixer(h) + feed_forward(h)  (the feed-forward may be absent).
+    Both sublayers add into the float residual stream, the mixer first."""
+
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer)
+        self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn) if spec.ffn is not None else None
+        if spec.ffn_norm is not None:
+            raise ValueError("the parallel arrangement has one norm; its feed-forward reads the mixer's")
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn) if p is not None]
+
+    def workspace(self):
+        return {"normed": (int(self.mixer_norm.params["width"]), "act")}
+
+    def forward(self, ctx, x, view, owns_cache=True):
+        h = ctx.buf("normed", x.shape[1])
+        self.mixer_norm.forward(ctx, x, h)
+        self.mixer.forward(ctx, h, x, view, owns_cache)
+        if self.ffn is not None:
+            self.ffn.forward(ctx, h, x)

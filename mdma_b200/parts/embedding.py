@@ -1,4 +1,5 @@
-"""Token embedding (x[t,:] = table[ids[t],:], src/backend/cpu.rs:370-384) and
+"""Token embedding (x[t,:] = table[ids[t],:], src/backend/cpu.rs:370-384; times `scale` where an
+architecture sets one) and
 the output head (logits = h W^T over the wanted rows only,
 src/model.rs:370-373, 462-467).  A tied head names the embedding's tensor."""
 from __future__ import annotations
@@ -15,6 +16,7 @@ class Embedding(Part):
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab, self.width = int(self.params["vocab_size"]), int(self.params["width"])
+        self.scale = float(self.params.get("scale", 1.0))      # the rows are multiplied by it, in float
 
     def tensor_specs(self):
         return {"weight": TensorSpec((self.vocab, self.width))}
@@ -24,7 +26,7 @@ class Embedding(Part):
         self.weight = tensors["weight"]
 
     def forward(self, ctx, ids, x):
-        ops.embed_rows(self.weight, ids, x)
+        ops.embed_rows(self.weight, ids, x, self.scale)
 
     def resident_tensors(self):
         return [self.weight]

@@ -10,6 +10,9 @@ it is added to the residual stream.
 
 Loop input: before a pass over a looped stack of layers, x <- W [x ; x0] + s_t,
 x0 the embedding's output and s_t a learned vector per pass.
+
+Loop add: the same place, without a matrix: x <- x + x0 (not before the first
+pass), then x <- x + s_t.
 """
 from __future__ import annotations
 
@@ -117,3 +120,27 @@ class LoopInput(Part):
 
     def resident_tensors(self):
         return [self.proj[0].w, self.step] if self.proj else [self.step]
+
+
+@JUNCTIONS.register("loop_add")
+class LoopAdd(Part):
+    """Before pass t of a looped stack: x <- (x + x0) + step[t] for t > 0, x <- x + step[0] for the first pass.
+    `step` is [passes, width]."""
+    needs_embedding = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width, self.passes = int(self.params["width"]), int(self.params["passes"])
+
+    def tensor_specs(self):
+        return {"step": TensorSpec((self.passes, self.width), "vector", "normal")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.step = tensors["step"]
+
+    def forward(self, ctx, x, x0, t: int):
+        ops.loop_add(x, x0 if t > 0 else None, self.step[t], ctx.n_tokens)
+
+    def resident_tensors(self):
+        return [self.step]

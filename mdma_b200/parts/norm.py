@@ -4,7 +4,10 @@ RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w (src/backend/cpu.rs:388-401;
 no +1 on the weight, no mean subtraction); sums in float.
 
 Dynamic tanh: y = tanh(alpha * x) * w + b with a learned scalar alpha; no mean,
-no variance, nothing summed over the row."""
+no variance, nothing summed over the row.
+
+Layer norm with a weight and no bias: y = (x - mean) / sqrt(var + eps) * w, var
+the mean of the squared deviations; sums in float."""
 from __future__ import annotations
 
 from .. import ops
@@ -74,3 +77,30 @@ class DynamicTanh(Part):
 
     def resident_tensors(self):
         return [self.weight, self.b, self.alpha]
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Part):
+    """(x - mean) / sqrt(var + eps) * w; no bias."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(self.params["width"])
+        self.eps = float(self.params["eps"])
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.width,), "vector")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors["weight"]
+
+    def forward(self, ctx, x, out, rows=None, n_rows=None):
+        n = n_rows if n_rows is not None else (None if rows is not None else ctx.n_tokens)
+        if self.rt.gemm == "tensor":
+            from .. import ops_tensor
+            ops_tensor.flush_pending(x.device, self.rt.tc)
+        ops.layernorm(x, self.weight, self.eps, out, rows, n)
+
+    def resident_tensors(self):
+        return [self.weight]

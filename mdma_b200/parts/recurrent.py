@@ -12,6 +12,13 @@ convolution per channel and silu; per head h (group h // (heads / G)),
 y * silu(z) is divided by its root mean square in `norm_groups` equal parts, weighted and
 sent through Wo.  State: S [heads, N, vdim] and the convolution's last taps-1 inputs.
 
+RG-LRU (`rglru`), a recurrent block with a real-gated linear recurrent unit: two branches of
+`width` channels, y = gelu_tanh(Wy h + by) and u = conv(Wx h + bx) (a short causal convolution per
+channel, no activation); u is cut into `blocks` equal parts, and in part b
+    r = sigmoid(Ra[b] u_b + ra_b),  i = sigmoid(Ri[b] u_b + ri_b)      (square matrices per part),
+    log a = -decay r softplus(lam),  S_t = a S_(t-1) + sqrt(1 - a^2) (i u),  out = Wo (S_t * y).
+State: S (`width` floats) and the convolution's last taps-1 inputs.  `decay` is 8 unless set.
+
 The state is float, zero at a sequence's start, kept per slot by the cache; everything
 that enters the recurrences is float in both engines (the projections write float rows).
 Both offer `produce` (the result as float rows) beside the ordinary `forward`.
@@ -193,3 +200,81 @@ class Mamba2(_StatefulMixer):
 
     def resident_tensors(self):
         return [self.w_in.w, self.o.w, self.conv_w, self.conv_b, self.dt_bias, self.a_log, self.d, self.norm]
+
+
+@MIXERS.register("rglru")
+class RGLRU(_StatefulMixer):
+    MAX_TAPS = 16
+    RUNS_FROM = 256           # rows in the step's longest sequence from which the side-by-side walk is used
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.width = int(p["hidden_size"]), int(p["width"])
+        self.blocks, self.taps = int(p["blocks"]), int(p["conv"])
+        self.decay = float(p.get("decay", 8.0))
+        if self.width % self.blocks:
+            raise ValueError(f"{self.width} channels do not divide into {self.blocks} blocks")
+        if not 1 <= self.taps <= self.MAX_TAPS:
+            raise ValueError(f"a convolution of {self.taps} taps is outside the kernel's 1..{self.MAX_TAPS}")
+        self.block_size = self.width // self.blocks
+        self.conv_floats = (self.taps - 1) * self.width
+
+    def tensor_specs(self):
+        w, h, b, n = self.width, self.hidden, self.blocks, self.block_size
+        vec = lambda: TensorSpec((w,), "vector", "normal")
+        return {"y": TensorSpec((w, h)), "y.b": vec(), "x": TensorSpec((w, h)), "x.b": vec(),
+                "conv": TensorSpec((w, self.taps)), "conv.b": vec(),
+                "ra": TensorSpec((b, n, n)), "ra.b": TensorSpec((b, n), "vector", "normal"),
+                "ri": TensorSpec((b, n, n)), "ri.b": TensorSpec((b, n), "vector", "normal"),
+                "lam": vec(), "o": TensorSpec((h, w))}
+
+    def fused_tensors(self):
+        return {"yx": ("y", "x"), "yx.b": ("y.b", "x.b")}          # one product for the two branches
+
+    def state_need(self):
+        return StateNeed((self.width + self.conv_floats,), torch.float32)
+
+    def workspace(self):
+        w = self.width
+        return {f"lru_p_{w}": (2 * w, "f32"), f"lru_u_{w}": (w, "f32"), f"lru_r_{w}": (w, "f32"),
+                f"lru_i_{w}": (w, "f32"), f"lru_s_{w}": (w, "act")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        fused, bias = tensors.get("yx"), tensors.get("yx.b")
+        if fused is None:
+            fused = torch.cat([tensors["y"], tensors["x"]], dim=0).contiguous()
+        if bias is None:
+            bias = torch.cat([tensors["y.b"], tensors["x.b"]]).contiguous()
+        self.yx = Linear(fused, rt, bias=bias)
+        self.o = Linear(tensors["o"], rt)
+        self.conv_w, self.conv_b = tensors["conv"], tensors["conv.b"]
+        self.ra, self.ri = tensors["ra"], tensors["ri"]
+        self.ra_b, self.ri_b = tensors["ra.b"].reshape(-1), tensors["ri.b"].reshape(-1)
+        self.lam = tensors["lam"]
+
+    def _run(self, ctx, h, target, view, accumulate, defer=False):
+        n, w = ctx.n_tokens, self.width
+        p = ctx.buf(f"lru_p_{w}", 2 * w, torch.float32)
+        u = ctx.buf(f"lru_u_{w}", w, torch.float32)
+        r = ctx.buf(f"lru_r_{w}", w, torch.float32)
+        i = ctx.buf(f"lru_i_{w}", w, torch.float32)
+        s = ctx.buf(f"lru_s_{w}", w)
+        lru_state = view.state[:, :w]
+        conv_state = view.state[:, w:w + self.conv_floats]
+        self.yx.store(h, p, n)                            # [y | x] with their biases, float rows
+        ops.causal_conv_silu(p, w, self.conv_w, self.conv_b, self.taps, w, ctx.tok_seq, ctx.seq_start, ctx.seq_slot,
+                             conv_state, u, n, ctx.n_seqs, silu=False)
+        # the gates' block-diagonal products read the float rows; float sums on the CUDA cores in both engines
+        ops.gemm_simt_batched(u, self.ra, r, n)
+        ops.gemm_simt_batched(u, self.ri, i, n)
+        # long prompts in the serving engine: runs of a sequence side by side; the 32-bit engine keeps the row-by-row
+        # order, so that its results do not depend on how a prompt was cut
+        runs = ctx.max_new >= self.RUNS_FROM and s.dtype != torch.float32
+        ops.rglru_scan(r, i, u, p[:, :w], self.ra_b, self.ri_b, self.lam, self.decay, ctx.seq_start, ctx.seq_slot,
+                       lru_state, s, ctx.n_seqs, w, runs)
+        self._finish(self.o, s, target, n, accumulate, defer)
+
+    def resident_tensors(self):
+        return [self.yx.w, self.yx.bias, self.o.w, self.conv_w, self.conv_b, self.ra, self.ri, self.ra_b, self.ri_b, self.lam]
