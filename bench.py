@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
     python bench.py --shape llama-2-7b | llama-3.2-1b [--batch B] [--prompt-len P] [--prefill-tokens T]
-    python bench.py --compare gevonex [--compare-widths 1024,2048,4096] [--compare-layers 4]
+    python bench.py --compare gevonex|mogevik [--compare-widths 1024,2048,4096] [--compare-layers 4]
 
 Prints ONE JSON line.  The default run has the layer sizes of the
 Llama-3.1-8B shape with random bfloat16 weights, a batch of 8 sequences
@@ -20,6 +20,11 @@ Gevonex architecture (recurrent and latent-attention mixers, random weights)
 at a few layer sizes, beside a Llama of the same width, depth and vocabulary,
 each with the share of the measured peaks it reaches.  It prints one JSON line
 of its own; the default workload and its line are unchanged.
+
+`--compare mogevik` does the same for the Mogevik architecture (RG-LRU and
+windowed attention with a distance penalty, routed feed-forwards) beside a
+Gevonex and a Llama of the same width, depth and vocabulary and the same
+number of matrix elements a token uses.
 """
 from __future__ import annotations
 
@@ -145,6 +150,37 @@ def gevonex_config(width: int, layers: int, vocab: int) -> dict:
                        for i in range(layers)]}
 
 
+def mogevik_config(width: int, layers: int, vocab: int) -> dict:
+    """A Mogevik of `layers` layers (two recurrent layers, then one of attention, ...) whose sizes follow the width:
+    a recurrence as wide as the model in blocks of 256 channels with four taps; query heads of 128 in groups of four
+    over a window of 1,024; fourteen experts of width / 2 and two identity experts in four groups of which three are
+    kept, four per token, and a shared expert of 2/3 width: the matrix elements a token uses are those of a dense
+    feed-forward of 4 x width."""
+    heads = max(1, width // 128)
+    kinds = ["rglru", "rglru", "attention"]
+    mixers = {"rglru": {"width": width, "blocks": max(1, width // 256), "conv": 4},
+              "attention": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                            "mask": {"size": 1024}}}
+    mlp = {"kind": "moe", "expert": {"ff": width // 2}, "shared": {"ff": (2 * width // 3 + 63) // 64 * 64},
+           "router": {"experts": 14, "identity": 2, "top": 4, "groups": {"count": 4, "keep": 3}}}
+    return {"architecture": "Mogevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5}, "loop": {"start": 0, "stop": layers, "times": 1},
+            "layers": [{"type": kinds[i % 3], "mixer": mixers[kinds[i % 3]], "mlp": mlp} for i in range(layers)]}
+
+
+def expert_share(cfg: dict, name: str, draws: int) -> float:
+    """The share of an expert's matrix that a step of `draws` tokens reads (decode: distinct experts among the
+    draws, chosen evenly) or, with draws = 0, the share of tokens that use it (prefill)."""
+    parts = name.split(".")
+    if len(parts) < 3 or parts[1] != "mlp" or not parts[2].startswith("e") or not parts[2][1:].isdigit():
+        return 1.0
+    router = cfg["layers"][int(parts[0][1:])]["mlp"]["router"]
+    n = router["experts"] + (router.get("identity") or 0)
+    if draws == 0:
+        return router["top"] / n
+    return 1.0 - (1.0 - 1.0 / n) ** (draws * router["top"])
+
+
 def llama_like(width: int, layers: int, vocab: int) -> dict:
     """The closest existing model at equal size: the same width, depth and vocabulary, heads of 128 in groups of
     four, a gated feed-forward of 8/3 x width (the same three-matrix parameter count as 4 x width ungated + gate)."""
@@ -169,10 +205,15 @@ def compare(args) -> int:
 
     def measure(cfg, batch):
         eng = Engine(config=cfg, seed=0, dtype=args.dtype, max_batch=batch, max_context=max(T, prompt + 512))
-        matrix_bytes = 0
+        matrix_bytes = prefill_elements = 0          # bytes a decode step reads; matrix elements a prompt token uses
         for name, ts in eng.model.expected_tensors().items():
-            if len(ts.shape) == 2 and "embed" not in name:
-                matrix_bytes += 2 * ts.shape[0] * ts.shape[1]
+            if len(ts.shape) >= 2 and ts.kind == "matrix" and "embed" not in name:
+                n = 1
+                for d in ts.shape:
+                    n *= d
+                routed = cfg.get("architecture") == "Mogevik"
+                matrix_bytes += 2 * n * (expert_share(cfg, name, batch) if routed else 1.0)
+                prefill_elements += n * (expert_share(cfg, name, 0) if routed else 1.0)
         # what a decode step moves besides the matrices: every live sequence's fixed-size state is read and written,
         # and its cached rows (keys and values, or latents) are read
         state_per_seq = eng.cache.state_bytes / eng.cache.max_slots
@@ -219,7 +260,7 @@ def compare(args) -> int:
         # share is a lower bound); decode: the matrices once, every sequence's state twice, its cached rows once
         return {"matrix_gb": round(matrix_bytes / 1e9, 3), "decode_gb_per_step": round(decode_bytes / 1e9, 3),
                 "prefill_tokens_per_s": round(T * 1000.0 / ms_p, 1), "prefill_ms": round(ms_p, 3),
-                "prefill_frac_of_bf16_peak": round(T * matrix_bytes / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4),
+                "prefill_frac_of_bf16_peak": round(2 * T * prefill_elements / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4),
                 "decode_tokens_per_s": round(batch * 1000.0 / ms_d, 1), "decode_ms_per_step": round(ms_d, 4),
                 "decode_frac_of_hbm_peak": round(decode_bytes / (ms_d * 1e-3) / 1e9 / hbm_gbs, 4),
                 "launches_per_decode_step": launches}
@@ -229,10 +270,13 @@ def compare(args) -> int:
     rows = []
     for width in [int(w) for w in args.compare_widths.split(",")]:
         row = {"width": width, "layers": args.compare_layers, "vocab": vocab, "batch": args.batch}
+        if args.compare == "mogevik":
+            row["mogevik"] = measure(mogevik_config(width, args.compare_layers, vocab), args.batch)
         row["gevonex"] = measure(gevonex_config(width, args.compare_layers, vocab), args.batch)
         row["llama"] = measure(llama_like(width, args.compare_layers, vocab), args.batch)
         rows.append(row)
-    print(json.dumps({"compare": "gevonex beside llama at equal width, depth and vocabulary", "dtype": args.dtype,
+    print(json.dumps({"compare": ("mogevik beside gevonex and llama" if args.compare == "mogevik" else "gevonex beside llama")
+                      + " at equal width, depth and vocabulary", "dtype": args.dtype,
                       "prefill_tokens": T, "decode_after_prompts_of": prompt, "peaks": peak_src,
                       "hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops,
                       "timing": "CUDA events; every step reads its matrices (0.15 GB and more at the default widths), more than the 126 MB of L2, so nothing is flushed",
@@ -259,7 +303,7 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the true 32-bit engine (CUDA-core kernels), for the record; the headline is bfloat16")
-    ap.add_argument("--compare", default=None, choices=["gevonex"],
+    ap.add_argument("--compare", default=None, choices=["gevonex", "mogevik"],
                     help="another program: the named architecture beside a Llama of equal size (see the header)")
     ap.add_argument("--compare-widths", default="1024,2048,4096")
     ap.add_argument("--compare-layers", type=int, default=4)

@@ -160,7 +160,7 @@ expert_down_kernel(const TA* __restrict__ act, const TA* __restrict__ h, int h_s
 // One block: the step's pairs are few enough for a serial scan per expert chunk (a thread per expert counts its own).
 __global__ void __launch_bounds__(256)
 expert_sort_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int* __restrict__ first,
-                   int* __restrict__ order) {
+                   int* __restrict__ order, int* __restrict__ where) {
     chain_release();
     chain_wait();
     __shared__ int counts[kMaxRouted + 1];
@@ -180,8 +180,26 @@ expert_sort_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, i
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
         int at = counts[e];
         for (int p = 0; p < n_pairs; ++p)
-            if (chosen[p] == e) order[at++] = p;
+            if (chosen[p] == e) {
+                if (where) where[p] = at;          // the inverse: where pair p stands in the sorted list
+                order[at++] = p;
+            }
     }
+}
+
+// rows[i] = h[order[i] / top] for the sorted pairs i < first[n_experts]: the experts' inputs, expert after expert,
+// as contiguous rows that a matrix product can take
+template <typename TA>
+__global__ void __launch_bounds__(256)
+expert_gather_kernel(const TA* __restrict__ h, int h_stride, const int* __restrict__ first, const int* __restrict__ order,
+                     int n_experts, int top, int width, TA* __restrict__ rows) {
+    chain_release();
+    chain_wait();
+    const int i = blockIdx.x;
+    if (i >= first[n_experts]) return;
+    const TA* src = h + (size_t)(order[i] / top) * h_stride;
+    TA* dst = rows + (size_t)i * width;
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) dst[e] = src[e];
 }
 
 // Tile sizes of the expert-by-expert products: kPairTile pairs x kFeatTile features per block, K walked kKTile at a time.
@@ -315,11 +333,13 @@ expert_down_sorted_kernel(const TA* __restrict__ act, const TW* __restrict__ D, 
     }
 }
 
-// x[t, f] += sum_j w[t, j] * (y[t * top + j, f]  or, for an identity expert,  h[t, f]), j in order
+// x[t, f] += sum_j w[t, j] * (y[row of pair t * top + j, f]  or, for an identity expert,  h[t, f]), j in order;
+// the row of a pair is the pair's number, or where[pair] when y holds the sorted list's rows
 template <typename TA>
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(const float* __restrict__ y, const TA* __restrict__ h, int h_stride, const int* __restrict__ chosen,
-                      const float* __restrict__ weights, int n_experts, int top, int width, float* __restrict__ x) {
+                      const float* __restrict__ weights, const int* __restrict__ where, int n_experts, int top, int width,
+                      float* __restrict__ x) {
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
@@ -328,7 +348,8 @@ expert_combine_kernel(const float* __restrict__ y, const TA* __restrict__ h, int
         for (int j = 0; j < top; ++j) {
             const int e = chosen[(size_t)t * top + j];
             if (e < 0) continue;
-            const float v = e >= n_experts ? to_float(h[(size_t)t * h_stride + f]) : y[((size_t)t * top + j) * width + f];
+            const size_t pair = (size_t)t * top + j;
+            const float v = e >= n_experts ? to_float(h[(size_t)t * h_stride + f]) : y[(where ? (size_t)where[pair] : pair) * width + f];
             total += weights[(size_t)t * top + j] * v;
         }
         x[(size_t)t * width + f] += total;
@@ -403,7 +424,7 @@ int mdma_experts_sorted(const void* h, int h_dtype, int h_stride, const void* G,
     const int wparts = (width + 255) / 256 > 64 ? 64 : (width + 255) / 256;
     MDMA_DISPATCH_2(h_dtype, TA, w_dtype, TW, {
         if (n_experts > 0) {
-            launch_chained(expert_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, n_experts, first, order);
+            launch_chained(expert_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, n_experts, first, order, (int*)nullptr);
             launch_chained(expert_gate_up_sorted_kernel<TA, TW>, dim3((ff + kFeatTile - 1) / kFeatTile, pair_tiles, n_experts),
                            dim3(256), 0, stream, (const TA*)h, h_stride, (const TW*)G, (const TW*)U, first, order, top, width,
                            ff, (TA*)act);
@@ -411,9 +432,39 @@ int mdma_experts_sorted(const void* h, int h_dtype, int h_stride, const void* G,
                            dim3(256), 0, stream, (const TA*)act, (const TW*)D, first, order, width, ff, y);
         }
         launch_chained(expert_combine_kernel<TA>, dim3(n_tokens, wparts), dim3(256), 0, stream, y, (const TA*)h, h_stride,
-                       chosen, weights, n_experts, top, width, x);
+                       chosen, weights, (const int*)nullptr, n_experts, top, width, x);
     });
     MDMA_LAUNCH_OK("experts_sorted");
+    return 0;
+}
+
+// The two ends of the expert-by-expert way when the products in between are the caller's (one matrix product per
+// expert over its run of gathered rows).  Sort and gather: first [n_experts + 1], order and where [n_tokens * top],
+// rows [n_tokens * top, width] in h's dtype.
+int mdma_experts_gather(const void* h, int h_dtype, int h_stride, const int* chosen, int n_tokens, int n_experts, int top,
+                        int width, int* first, int* order, int* where, void* rows, cudaStream_t stream) {
+    MDMA_REQUIRE(n_tokens >= 0 && width > 0 && top > 0 && n_experts > 0 && n_experts <= kMaxRouted, "experts: bad sizes");
+    if (n_tokens == 0) return 0;
+    const int n_pairs = n_tokens * top;
+    const int wparts = (width + 255) / 256 > 64 ? 64 : (width + 255) / 256;
+    launch_chained(expert_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, n_experts, first, order, where);
+    MDMA_DISPATCH_DTYPE(h_dtype, TA,
+        launch_chained(expert_gather_kernel<TA>, dim3(n_pairs, wparts), dim3(256), 0, stream, (const TA*)h, h_stride,
+                       (const int*)first, (const int*)order, n_experts, top, width, (TA*)rows));
+    MDMA_LAUNCH_OK("experts_gather");
+    return 0;
+}
+
+// Combine: y [sorted rows, width] floats hold the experts' results in the sorted list's order.
+int mdma_experts_combine(const float* y, const void* h, int h_dtype, int h_stride, const int* chosen, const float* weights,
+                         const int* where, int n_tokens, int n_experts, int top, int width, float* x, cudaStream_t stream) {
+    MDMA_REQUIRE(n_tokens >= 0 && width > 0 && top > 0, "experts: bad sizes");
+    if (n_tokens == 0) return 0;
+    const int wparts = (width + 255) / 256 > 64 ? 64 : (width + 255) / 256;
+    MDMA_DISPATCH_DTYPE(h_dtype, TA,
+        launch_chained(expert_combine_kernel<TA>, dim3(n_tokens, wparts), dim3(256), 0, stream, y, (const TA*)h, h_stride,
+                       chosen, weights, where, n_experts, top, width, x));
+    MDMA_LAUNCH_OK("experts_combine");
     return 0;
 }
 

@@ -572,3 +572,26 @@ def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: 
     _call("core", "mdma_experts_sorted", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(gate_w), _ptr(up_w),
           _ptr(down_w), _i(wd), _ptr(chosen), _ptr(weights), _i(n_tokens), _i(n_experts), _i(top), _i(width), _i(ff),
           _ptr(first), _ptr(order), _ptr(act), _ptr(y), _ptr(x), _stream(), launches=4)
+
+
+def experts_gather(h, chosen, n_tokens: int, n_experts: int, top: int, first, order, where, rows) -> None:
+    """Sort the (token, choice) pairs by expert (first [n_experts + 1], order and its inverse `where` [tokens * top])
+    and copy each sorted pair's input row to `rows` [tokens * top, width], expert after expert."""
+    _need_cuda(h, chosen, first, order, where, rows)
+    width = h.shape[1]
+    assert h.stride(1) == 1 and rows.is_contiguous() and rows.dtype == h.dtype and rows.shape[1] == width
+    assert first.dtype == order.dtype == where.dtype == chosen.dtype == torch.int32
+    assert first.numel() >= n_experts + 1 and order.numel() >= n_tokens * top and where.numel() >= n_tokens * top
+    assert rows.shape[0] >= n_tokens * top
+    _call("core", "mdma_experts_gather", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(chosen), _i(n_tokens),
+          _i(n_experts), _i(top), _i(width), _ptr(first), _ptr(order), _ptr(where), _ptr(rows), _stream(), launches=2)
+
+
+def experts_combine(y, h, chosen, weights, where, n_tokens: int, n_experts: int, top: int, x) -> None:
+    """x[t] += sum_j weights[t, j] * (y[where[t * top + j]] or, for an identity expert, h[t]); y float rows in the
+    sorted list's order."""
+    _need_cuda(y, h, chosen, weights, where, x)
+    width = h.shape[1]
+    assert y.dtype == torch.float32 and y.is_contiguous() and x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == width
+    _call("core", "mdma_experts_combine", _ptr(y), _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(chosen),
+          _ptr(weights), _ptr(where), _i(n_tokens), _i(n_experts), _i(top), _i(width), _ptr(x), _stream())

@@ -14,7 +14,11 @@ Tensors: `e<i>.gate|up|down`, `router` [experts + identity, width], `correction`
 matrices, so that a kernel finds expert e at a row offset.
 
 Steps of few tokens read each chosen expert's matrices token by token; steps of many tokens sort the
-(token, choice) pairs by expert on the device and compute expert by expert.  Nothing is read on the host.
+(token, choice) pairs by expert on the device and compute expert by expert.  Nothing is read on the host
+there.  Prompts of the serving engine (steps of `PRODUCTS_FROM` tokens or more that are not a replayed
+decode step) gather each expert's input rows and run ONE tensor-core product pair per expert over its
+run of rows; how many rows an expert got is read back from the device for that (the only host read of
+this part; a replayed step never takes this way).
 """
 from __future__ import annotations
 
@@ -32,6 +36,7 @@ class RoutedMLP(Part):
     graph_safe = True
     MAX_ROUTED, MAX_TOP = 1024, 32       # the router kernel's limits
     SORTED_FROM = 33                     # tokens in a step from which the serving engine computes expert by expert
+    PRODUCTS_FROM = 128                  # tokens in a step from which it does so with a matrix product per expert
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -80,12 +85,14 @@ class RoutedMLP(Part):
     def _names(self):
         tag = f"{self.top}_{self.ff}_{self.hidden}"
         return (f"routed_chosen_{tag}", f"routed_weight_{tag}", f"routed_order_{tag}", f"routed_act_{tag}",
-                f"routed_y_{tag}", f"routed_shared_{self.shared_ff}", "routed_scale")
+                f"routed_y_{tag}", f"routed_shared_{self.shared_ff}", "routed_scale", f"routed_where_{tag}",
+                f"routed_rows_{tag}")
 
     def workspace(self):
-        chosen, weight, order, act, y, shared, scale = self._names()
-        ws = {chosen: (self.top, "f32"), weight: (self.top, "f32"), order: (self.top, "f32"),
-              act: (self.top * self.ff, "act"), y: (self.top * self.hidden, "f32"), scale: (1, "f32")}
+        chosen, weight, order, act, y, shared, scale, where, rows = self._names()
+        ws = {chosen: (self.top, "f32"), weight: (self.top, "f32"), order: (self.top, "f32"), where: (self.top, "f32"),
+              act: (self.top * self.ff, "act"), y: (self.top * self.hidden, "f32"), scale: (1, "f32"),
+              rows: (self.top * self.hidden, "act")}
         if self.shared_ff:
             ws[shared] = (self.shared_ff, "act")
         return ws
@@ -110,6 +117,12 @@ class RoutedMLP(Part):
             if self.shared_gate:
                 self.sg = tensors["shared.sg"].reshape(-1)
         self.first = rt.derived(torch.zeros(self.n_experts + 1, dtype=torch.int32))
+        # a product pair per expert, over views of the stacked matrices (the tensor-core way of long prompts)
+        self.expert_up, self.expert_down = [], []
+        if self.n_experts and rt.gemm == "tensor":
+            F, W = self.ff, self.hidden
+            self.expert_up = [Linear(self.w_gate[e * F:(e + 1) * F], rt, self.w_up[e * F:(e + 1) * F]) for e in range(self.n_experts)]
+            self.expert_down = [Linear(self.w_down[e * W:(e + 1) * W], rt) for e in range(self.n_experts)]
 
     def forward(self, ctx, h, x):
         n = ctx.n_tokens
@@ -123,6 +136,11 @@ class RoutedMLP(Part):
         scale = ctx.buf(names[6], 1, torch.float32)
         ops.route(h, self.router, self.correction_values, self.sg, n, self.top, self.groups, self.keep_groups, chosen,
                   weight, scale if self.sg is not None else None)
+        if (self.expert_up and n >= self.PRODUCTS_FROM and not getattr(ctx, "decode_only", False)
+                and not torch.cuda.is_current_stream_capturing()):
+            self._experts_by_products(ctx, h, x, chosen, weight, act, names)
+            self._shared(ctx, h, x, scale)
+            return
         # the 32-bit engine keeps ONE order of additions whatever the step's size: always expert by expert
         scratch = None
         if act.dtype == torch.float32 or n >= self.SORTED_FROM:
@@ -130,8 +148,28 @@ class RoutedMLP(Part):
             scratch = (self.first, order, ctx.buf(names[4], self.top * self.hidden, torch.float32))
         ops.experts(h, self.w_gate, self.w_up, self.w_down, chosen, weight, n, self.n_experts, self.top, self.ff,
                     act.view(-1, self.ff), x, scratch)
+        self._shared(ctx, h, x, scale)
+
+    def _experts_by_products(self, ctx, h, x, chosen, weight, act, names):
+        n = ctx.n_tokens
+        order = ctx.buf(names[2], self.top, torch.float32).view(torch.int32)
+        where = ctx.buf(names[7], self.top, torch.float32).view(torch.int32)
+        y = ctx.buf(names[4], self.top * self.hidden, torch.float32).view(-1, self.hidden)
+        rows = ctx.buf(names[8], self.top * self.hidden).view(-1, self.hidden)
+        act = act.view(-1, self.ff)
+        ops.experts_gather(h, chosen, n, self.n_experts, self.top, self.first, order, where, rows)
+        first = self.first.tolist()                          # how many rows each expert got: read on the host
+        for e in range(self.n_experts):
+            lo, m = first[e], first[e + 1] - first[e]
+            if m:
+                self.expert_up[e].gated(rows[lo:lo + m], act[lo:lo + m], m)
+                self.expert_down[e].store(act[lo:lo + m], y[lo:lo + m], m)
+        ops.experts_combine(y, h, chosen, weight, where, n, self.n_experts, self.top, x)
+
+    def _shared(self, ctx, h, x, scale):
+        n = ctx.n_tokens
         if self.shared_ff:
-            sact = ctx.buf(names[5], self.shared_ff)
+            sact = ctx.buf(self._names()[5], self.shared_ff)
             self.shared_up.gated(h, sact, n)
             if self.sg is not None:
                 ops.scale_rows(sact, scale.view(-1), n)      # the down product is linear: scaling its input scales its result

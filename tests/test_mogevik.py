@@ -1,0 +1,825 @@
+"""The Mogevik architecture against its plain statement (tests/plain_mogevik.py): every mechanism alone
+through its kernel, then whole models through the engine's step function, the cache and state manager,
+the scheduler and the generation loop.  Configurations and weights are made here (tests/mogevik_tiny.py)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_mogevik as pm
+from mogevik_tiny import CFG_A, CFG_B, CFG_C, CFG_D, CFG_E, make_model, make_tensors
+
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
+# float32: absolute, against the float64 statement.  bfloat16: the largest error as a share of the deviation of the
+# reference logits, and a row's root-mean-square error as a share of the row's own deviation.
+TOL_F32 = 5e-5
+TOL_BF16, TOL_ROW_BF16 = 0.12, 0.04
+TOL_BF16_DRAWN, TOL_ROW_BF16_DRAWN = 0.4, 0.15
+
+
+def ids_of(cfg, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, cfg["vocab"], (n,), generator=g).tolist()
+
+
+_largest = {}        # the largest errors seen, printed at exit when MOGEVIK_TEST_REPORT is set
+_rows = {"checked": 0, "off": 0}
+
+
+def close(got, ref, dtype, what="", drawn=False):
+    """float32: every logit within TOL_F32 of the float64 statement.  bfloat16: every row within the tolerances, except
+    rows where a router's close call fell the other way: bfloat16 rounding upstream moves choice scores by ~1e-3 and a
+    token whose last chosen and first unchosen expert are closer than that takes another expert, which moves that row
+    (and hardly any other) by a good part of its deviation.  Such rows are counted: at most one in twelve of a call's
+    rows (or one), at most 5 % + 4 of all rows checked so far, and the median row must be well inside the tolerance."""
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    assert np.isfinite(got).all(), f"{what}: logits that are not finite"
+    err = np.abs(got - ref)
+    if dtype == "float32":
+        _largest[dtype] = max(_largest.get(dtype, 0.0), float(err.max()))
+        assert err.max() < TOL_F32, f"{what}: {err.max()}"
+        return
+    tol, tol_row = (TOL_BF16_DRAWN, TOL_ROW_BF16_DRAWN) if drawn else (TOL_BF16, TOL_ROW_BF16)
+    key = "drawn " if drawn else ""
+    err2, ref2 = np.atleast_2d(err), np.atleast_2d(ref)
+    share = err2.max(axis=-1) / max(float(ref.std()), 0.25)
+    rel = np.sqrt((err2 ** 2).mean(axis=-1)) / np.maximum(ref2.std(axis=-1), 1e-3)
+    off = (share >= tol) | (rel >= tol_row)
+    fine = ~off
+    if fine.any():
+        _largest[key + dtype] = max(_largest.get(key + dtype, 0.0), float(share[fine].max()))
+        _largest[key + "row"] = max(_largest.get(key + "row", 0.0), float(rel[fine].max()))
+    _rows["checked"] += len(off)
+    _rows["off"] += int(off.sum())
+    assert off.sum() <= max(1, len(off) // 12), f"{what}: {int(off.sum())} of {len(off)} rows are off (largest share {share.max()}, row error {rel.max()})"
+    assert _rows["off"] <= 0.05 * _rows["checked"] + 4, f"{what}: {_rows} rows off so far"
+    assert np.median(rel) < tol_row / 3, f"{what}: median row error {np.median(rel)}"
+
+
+if os.environ.get("MOGEVIK_TEST_REPORT"):
+    import atexit
+    atexit.register(lambda: print("largest errors seen:", _largest, "rows:", _rows))
+
+
+# =====================================================================================================
+# Without a GPU: configuration, description, and that the plain statement itself notices each mechanism.
+
+def test_config_is_read_and_checked():
+    from mdma_b200.config import ConfigError, load_config
+    arch, c = load_config(CFG_A)
+    assert arch.name == "Mogevik" and c.width == 64 and c.loop_times == 3 and c.layers[2].mlp is None
+    assert c.embedding_scale == 4.0 and c.layers[2].mixer["window"] == 37 and c.layers[0].mlp.groups == 1
+    assert c.layers[1].mlp.identity == 2 and c.layers[1].mlp.keep == 2 and c.layers[0].mlp.shared_ff == 0
+    spec = arch.describe(c)
+    runs = [(e.layer, e.junction, e.junction_arg) for e in spec.schedule]
+    assert runs == [(0, None, 0), (1, 0, 0), (2, None, 0), (1, 0, 1), (2, None, 0), (1, 0, 2), (2, None, 0), (3, None, 0)]
+    assert pm.schedule(CFG_A) == [(l, a if j is not None else None) for l, j, a in runs]
+    _, b = load_config(CFG_B)
+    assert b.loop_times == 0 and not arch.describe(b).junctions and b.layers[1].mixer["window"] == 0
+    for breaker in (lambda d: d.pop("width"),
+                    lambda d: d["layers"][0].update(type="lstm"),
+                    lambda d: d["layers"][1]["mixer"].pop("blocks"),
+                    lambda d: d["layers"][1]["mixer"].update(blocks=7),
+                    lambda d: d["layers"][0]["mlp"].update(kind="dense"),
+                    lambda d: d["layers"][1]["mlp"]["router"].update(top=9),
+                    lambda d: d["layers"][1]["mlp"]["router"]["groups"].update(count=3),
+                    lambda d: d["layers"][2]["mixer"].update(kv_heads=4),
+                    lambda d: d["loop"].update(stop=9), lambda d: d["loop"].update(times=0)):
+        bad = json.loads(json.dumps(CFG_A))
+        breaker(bad)
+        with pytest.raises(ConfigError):
+            load_config(bad)
+
+
+def test_tensor_inventory_and_plan_without_a_device(tmp_path):
+    from mdma_b200.config import load_config
+    from mdma_b200.engine.model import DecoderModel
+    from mdma_b200.engine.step import plan_only
+    arch, c = load_config(CFG_A)
+    model = DecoderModel(arch.describe(c))
+    names = set(model.expected_tensors())
+    assert {"embed", "final.norm", "loop.step", "l0.norm1", "l0.mix.q.b", "l0.mix.g", "l0.mlp.e4.down", "l0.mlp.router",
+            "l0.mlp.correction", "l1.mix.ra.b", "l1.mix.lam", "l1.mix.conv.b", "l1.mlp.shared.sg", "l1.mlp.e5.up",
+            "l3.mlp.shared.down"} <= names
+    assert "head" not in names and "l2.mlp.router" not in names and "l0.mlp.shared.sg" not in names
+    assert "l1.mlp.e6.up" not in names                      # identity experts have no tensors
+    assert model.expected_tensors()["l1.mlp.router"].shape == (8, 64)
+    # every run of a looped layer owns its state or its cache
+    state, kv = model.state_needs(), model.kv_needs()
+    assert [n is not None for n in state] == [False, True, False, True, False, True, False, True]
+    assert [n is not None for n in kv] == [True, False, True, False, True, False, True, False]
+    assert state[1].shape == (80 + 2 * 80,) and state[7].shape == (48 + 48,)
+    assert kv[2].head_dim == 16 and kv[2].v_dim == 24 and kv[2].n_kv_heads == 2 and kv[2].window == 37 and kv[0].v_dim == 0
+    d, _ = make_model(CFG_A, 3, root=str(tmp_path))
+    plan = plan_only(d, dtype="float32", max_batch=2, max_context=128)
+    assert plan["total_bytes"] > 0 and plan["cache_bytes"] > 0
+
+
+def test_the_plain_statement_notices_each_mechanism():
+    """Leaving a mechanism out of the plain statement moves the logits by far more than any tolerance here."""
+    W = make_tensors(CFG_A, 5)
+    ids = ids_of(CFG_A, 60, 1)
+    ref = pm.forward(CFG_A, W, ids)
+
+    def moved(changes=None, skip=None):
+        W2 = dict(W)
+        W2.update(changes or {})
+        return float((pm.forward(CFG_A, W2, ids, skip=skip) - ref).abs().max())
+    for skip in ("embedding_scale", "loop_embedding", "loop_step", "slopes", "window", "groups", "shared"):
+        assert moved(skip=skip) > 0.05, skip
+    assert moved({"l1.mlp.correction": torch.zeros_like(W["l1.mlp.correction"])}) > 0.05      # who is chosen changes
+    assert moved({"l0.mix.q.b": torch.zeros_like(W["l0.mix.q.b"])}) > 0.02
+    assert moved({"l2.mix.g": torch.zeros_like(W["l2.mix.g"])}) > 0.05                        # gate always half open
+    assert moved({"l1.mlp.shared.sg": torch.zeros_like(W["l1.mlp.shared.sg"])}) > 0.02
+    conv = W["l1.mix.conv"].clone()
+    conv[:, :-1] = 0
+    assert moved({"l1.mix.conv": conv}) > 0.05                                                # no taps back
+    assert moved({"l1.mix.lam": W["l1.mix.lam"] + 8.0}) > 0.02                                # a state that forgets at once
+    assert moved({"l1.mix.ri.b": W["l1.mix.ri.b"] + 30.0}) > 0.02                             # input gate always open
+    # identity experts return their input: with them taken for experts of zero output the result differs
+    chosen, _, _ = pm.route(torch.randn(50, 64, dtype=torch.float64), {k: v.double() for k, v in W.items()}, "l1.mlp.",
+                            CFG_A["layers"][1]["mlp"]["router"])
+    assert (chosen >= 6).any() and (chosen < 6).any()
+
+
+# =====================================================================================================
+# Kernels alone (GPU).
+
+def _dev(t, dtype=torch.float32):
+    return t.to(device="cuda", dtype=dtype).contiguous()
+
+
+def _i32(a):
+    return torch.as_tensor(np.asarray(a, dtype=np.int32), device="cuda")
+
+
+def _meta(lengths, slots):
+    starts = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    tok_seq = np.concatenate([np.full(n, s, dtype=np.int32) for s, n in enumerate(lengths)])
+    return _i32(tok_seq), _i32(starts), _i32(slots)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layer_norm_embedding_scale_loop_add_and_row_scale(dtype):
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    for width in (36, 64, 1000):
+        x = torch.randn(9, width, generator=g) * 3 + 1.5
+        w = (1 + 0.3 * torch.randn(width, generator=g)).to(dtype)
+        out = torch.empty(9, width, device="cuda", dtype=dtype)
+        ops.layernorm(_dev(x), _dev(w, dtype), 1e-5, out)
+        want = pm.layer_norm(x.double(), w.double(), 1e-5)
+        tol = 1e-5 if dtype == torch.float32 else 3e-2
+        assert (out.double().cpu() - want).abs().max() < tol
+        rows = [7, 2, 2]
+        ops.layernorm(_dev(x), _dev(w, dtype), 1e-5, out, _i32(rows), 3)
+        assert (out[:3].double().cpu() - want[rows]).abs().max() < tol
+        # the re-entry of a loop: with and without the embedding's rows
+        x0, step = torch.randn(9, width, generator=g), torch.randn(2, width, generator=g).to(dtype)
+        xd = _dev(x)
+        ops.loop_add(xd, None, _dev(step, dtype)[0], 9)
+        assert (xd.cpu() - (x + step[0].float())).abs().max() < 1e-6
+        ops.loop_add(xd, _dev(x0), _dev(step, dtype)[1], 9)
+        assert (xd.cpu() - (x + step[0].float() + x0 + step[1].float())).abs().max() < 1e-5
+        v, s = torch.randn(9, width, generator=g).to(dtype), torch.rand(9, generator=g)
+        vd = _dev(v, dtype)
+        ops.scale_rows(vd, _dev(s), 9)
+        assert (vd.double().cpu() - v.double() * s.double()[:, None]).abs().max() < (1e-6 if dtype == torch.float32 else 2e-2)
+    table = torch.randn(20, 40, generator=g).to(dtype)
+    out = torch.empty(5, 40, device="cuda")
+    ops.embed_rows(_dev(table, dtype), _i32([3, 19, 0, 3, 7]), out, 2.75)
+    assert (out.cpu().double() - table.double()[[3, 19, 0, 3, 7]] * 2.75).abs().max() < 1e-6
+
+
+def _plain_lru(r_pre, i_pre, u, y, rb, ib, lam, decay, S0):
+    """Row by row in float64 from state S0: (outputs [T, C], last S)."""
+    r, i = torch.sigmoid(r_pre + rb), torch.sigmoid(i_pre + ib)
+    log_a = -decay * r * torch.nn.functional.softplus(lam)
+    S, rows = S0.clone(), []
+    for t in range(u.shape[0]):
+        S = torch.exp(log_a[t]) * S + torch.sqrt(-torch.expm1(2 * log_a[t])) * i[t] * u[t]
+        rows.append(S * pm.gelu_tanh(y[t]))
+    return torch.stack(rows), S
+
+
+@pytest.mark.gpu
+def test_convolution_without_activation_and_recurrence_in_portions():
+    """Three sequences in slots out of order, each brought in portions down to one and two rows; the state rows hold
+    [S | kept inputs]; the outputs and the final state equal the whole-sequence walk; a slot used again starts clean."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    C, taps, decay = 44, 4, 8.0
+    lengths, slots = [23, 5, 40], [4, 0, 2]
+    w, b = torch.randn(C, taps, generator=g) * 0.6, torch.randn(C, generator=g) * 0.3
+    rb, ib, lam = (torch.randn(C, generator=g) for _ in range(3))
+    seqs = [{k: torch.randn(n, C, generator=g) for k in ("x", "r", "i", "y")} for n in lengths]
+    state = torch.full((6, C + (taps - 1) * C + 3), float("nan"), device="cuda")
+    state[:, :C + (taps - 1) * C] = 0
+    plans = [[2, 1, 17, 3], [5], [1, 1, 2, 30, 6]]
+    got = [[] for _ in seqs]
+    at = [0, 0, 0]
+    for step in range(5):
+        live = [s for s in range(3) if step < len(plans[s])]
+        ns = [plans[s][step] for s in live]
+        tok_seq, starts, slot_t = _meta(ns, [slots[s] for s in live])
+        cat = lambda k: _dev(torch.cat([seqs[s][k][at[s]:at[s] + n] for s, n in zip(live, ns)]))
+        T = sum(ns)
+        u = torch.empty(T, C, device="cuda")
+        ops.causal_conv_silu(cat("x"), 0, _dev(w), _dev(b), taps, C, tok_seq, starts, slot_t, state[:, C:C + (taps - 1) * C],
+                             u, T, len(live), silu=False)
+        out = torch.empty(T, C, device="cuda")
+        ops.rglru_scan(cat("r"), cat("i"), u, cat("y"), _dev(rb), _dev(ib), _dev(lam), decay, starts, slot_t, state[:, :C],
+                       out, len(live), C)
+        o = 0
+        for s, n in zip(live, ns):
+            got[s].append(out[o:o + n].double().cpu())
+            o += n
+            at[s] += n
+    for s, n in enumerate(lengths):
+        u = pm.causal_conv(seqs[s]["x"].double(), w.double(), b.double())
+        want, S = _plain_lru(seqs[s]["r"].double(), seqs[s]["i"].double(), u, seqs[s]["y"].double(), rb.double(), ib.double(),
+                             lam.double(), decay, torch.zeros(C, dtype=torch.float64))
+        assert (torch.cat(got[s]) - want).abs().max() < 2e-5, s
+        assert (state[slots[s], :C].double().cpu() - S).abs().max() < 2e-5
+        kept = state[slots[s], C:C + (taps - 1) * C].cpu().view(taps - 1, C)
+        assert torch.equal(kept, seqs[s]["x"][-(taps - 1):])
+    assert torch.isnan(state[:, C + (taps - 1) * C:]).all()            # nothing beyond a state row's own part is touched
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_recurrence_walked_as_runs_side_by_side(out_dtype):
+    """Long rows in one step: the side-by-side walk equals the row-by-row walk up to rounding, from a state that is
+    not zero, for a channel count that is no multiple of the block's eight and lengths that do not divide into runs."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    C, decay = 43, 8.0
+    lengths, slots = [700, 129, 1, 300], [1, 3, 0, 2]
+    T = sum(lengths)
+    r, i, u, y = (torch.randn(T, C, generator=g) for _ in range(4))
+    rb, ib = torch.randn(C, generator=g), torch.randn(C, generator=g)
+    lam = -4.5 + 5 * torch.rand(C, generator=g)
+    S0 = torch.randn(4, C, generator=g)
+    _, starts, slot_t = _meta(lengths, slots)
+    outs, states = [], []
+    for runs in (False, True):
+        state = _dev(S0)
+        out = torch.empty(T, C, device="cuda", dtype=out_dtype)
+        ops.rglru_scan(_dev(r), _dev(i), _dev(u), _dev(y), _dev(rb), _dev(ib), _dev(lam), decay, starts, slot_t, state, out,
+                       len(lengths), C, runs)
+        outs.append(out.double().cpu())
+        states.append(state.double().cpu())
+    o = 0
+    for s, n in enumerate(lengths):
+        sl = slice(o, o + n)
+        want, S = _plain_lru(r[sl].double(), i[sl].double(), u[sl].double(), y[sl].double(), rb.double(), ib.double(),
+                             lam.double(), decay, S0[slots[s]].double())
+        tol = 3e-5 if out_dtype == torch.float32 else 3e-2
+        for k in range(2):
+            assert (outs[k][sl] - want).abs().max() < tol, (s, k)
+            assert (states[k][slots[s]] - S).abs().max() < 3e-5, (s, k)
+        o += n
+
+
+def _plain_attention(q, k, v, gate, slopes, scale, window, pos0):
+    """q [n, H, D] at positions pos0.., k [L, G, D], v [L, G, V] (the whole sequence), gate [n, H, V] or None."""
+    n, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(n, H, v.shape[2], dtype=torch.float64)
+    for r in range(n):
+        i = pos0 + r
+        lo = max(0, i + 1 - window) if window else 0
+        for h in range(H):
+            kv = h // (H // G)
+            dist = (i - torch.arange(lo, i + 1)).double()
+            s = (k[lo:i + 1, kv] @ q[r, h]) * scale - slopes[h] * dist
+            out[r, h] = torch.softmax(s, 0) @ v[lo:i + 1, kv]
+    if gate is not None:
+        out = out * torch.sigmoid(gate)
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("H,G,D,V,window", [(3, 3, 16, 16, 0), (6, 2, 24, 40, 37), (4, 1, 40, 8, 64), (8, 4, 72, 20, 129)])
+def test_attention_kernels_far_key_window_edges_and_pages(dtype, tiled, H, G, D, V, window):
+    """A cache of scattered 16-row pages with NaN in every row nobody owns.  The prompt comes in two portions (a long
+    one, then the rest on the cached prefix) and the last rows again one by one.  One far key (position 3) is made to
+    stand out for the last query of head 1; the key at the window's edge is asked for by the query that still sees it
+    and by the next one, which must not."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(4 + H)
+    T, page, scale = 200, 16, 0.3
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float64)
+    k = torch.randn(T, G, D, generator=g).to(dtype).double()
+    v = torch.randn(T, G, V, generator=g).to(dtype).double()
+    q = torch.randn(T, H, D, generator=g) * 0.5
+    gate = torch.randn(T, H, V, generator=g).to(dtype).double()
+    far = 3
+    # coordinate 0 of the keys is zero except at the far key, coordinate 1 except at the window's edge key: a query
+    # along one of them scores that key alone, loudly enough to beat the penalty on its distance by e^12
+    k[:, :, 0] = 0
+    k[:, :, 1] = 0
+    k[far, 1 // (H // G), 0] = 8.0
+    q[T - 1, 1] = 0
+    q[T - 1, 1, 0] = float((12.0 + slopes[1] * T) / (8.0 * scale))
+    if window:
+        edge = T - 1 - window          # seen from row T-2 (distance window-1), not from row T-1
+        k[edge, 0, 1] = 8.0
+        q[T - 2, 0] = 0
+        q[T - 2, 0, 1] = float((12.0 + slopes[0] * T) / (8.0 * scale))
+        q[T - 1, 0] = q[T - 2, 0]
+    q = q.to(dtype).double()
+    n_pages, max_pages = 40, 13
+    perm = torch.randperm(n_pages, generator=g)[:max_pages].to(torch.int32)
+    kc = torch.full((n_pages, page, G, D), float("nan"), dtype=dtype, device="cuda")
+    vc = torch.full((n_pages, page, G, V), float("nan"), dtype=dtype, device="cuda")
+    table = torch.zeros(5, max_pages, dtype=torch.int32)
+    table[2] = perm
+    table = table.cuda()
+    want = _plain_attention(q, k, v, gate, slopes, scale, window, 0)
+    got = torch.empty(T, H, V, dtype=torch.float64)
+    from test_gevonex import _Step
+    portions = [150, 44] + [1] * 6
+    at = 0
+    for n in portions:
+        step = _Step([n], [at], [2])
+        proj = torch.cat([q[at:at + n].reshape(n, -1), k[at:at + n].reshape(n, -1), v[at:at + n].reshape(n, -1)], 1)
+        proj = _dev(proj, dtype)
+        ops.kv_store(proj, H * D, H * D + G * D, G * D, G * V, step.tok_seq, step.tok_pos, step.seq_slot, table, max_pages,
+                     page, kc, vc, n)
+        out = torch.empty(n, H * V, device="cuda", dtype=dtype)
+        ops.attention_distance(proj, kc, vc, step, table, max_pages, page, _dev(slopes), _dev(gate[at:at + n].reshape(n, -1), dtype),
+                               out, H, G, D, V, window, scale, tiled)
+        got[at:at + n] = out.double().cpu().view(n, H, V)
+        at += n
+    assert torch.isfinite(got).all()
+    tol = 3e-5 if dtype == torch.float32 else 4e-2
+    assert (got - want).abs().max() < tol
+    plain = _plain_attention(q, k, v, None, slopes, scale, window, 0)
+    if not window:      # the far key carries the last query's head 1
+        assert (plain[T - 1, 1] - v[far, 1 // (H // G)]).abs().max() < 0.05 * v[far].abs().max()
+    else:               # the edge key is seen from T-2 and not from T-1; the far key is outside every window
+        assert (plain[T - 2, 0] - v[edge, 0]).abs().max() < 0.05 * v[edge, 0].abs().max()
+        assert (plain[T - 1, 0] - v[edge, 0]).abs().max() > 0.2 * v[edge, 0].abs().max()
+
+
+@pytest.mark.gpu
+def test_attention_batch_of_unequal_sequences_equals_each_alone():
+    """Four sequences of different lengths and cached prefixes in one call, on both kernels, against each alone; the
+    plain kernel gives the same bits either way."""
+    from mdma_b200 import ops
+    from test_gevonex import _Step
+    g = torch.Generator().manual_seed(9)
+    H, G, D, V, window, page, scale = 4, 2, 16, 24, 21, 16, 0.25
+    slopes = _dev(torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]))
+    prefix, new, slots = [0, 30, 65, 7], [40, 1, 19, 2], [3, 0, 1, 2]
+    max_pages = 8
+    table = torch.arange(4 * max_pages, dtype=torch.int32).view(4, max_pages).flip(0).contiguous().cuda()
+    kc = torch.full((40, page, G, D), float("nan"), device="cuda")
+    vc = torch.full((40, page, G, V), float("nan"), device="cuda")
+    rows = [torch.randn(p + n, H * D + G * D + G * V, generator=g) for p, n in zip(prefix, new)]
+    for s in range(4):
+        if prefix[s]:
+            st = _Step([prefix[s]], [0], [slots[s]])
+            ops.kv_store(_dev(rows[s][:prefix[s]]), H * D, H * D + G * D, G * D, G * V, st.tok_seq, st.tok_pos, st.seq_slot,
+                         table, max_pages, page, kc, vc, prefix[s])
+    st = _Step(new, prefix, slots)
+    proj = _dev(torch.cat([rows[s][prefix[s]:] for s in range(4)]))
+    ops.kv_store(proj, H * D, H * D + G * D, G * D, G * V, st.tok_seq, st.tok_pos, st.seq_slot, table, max_pages, page, kc, vc,
+                 sum(new))
+    both = {}
+    for tiled in (False, True):
+        out = torch.empty(sum(new), H * V, device="cuda")
+        ops.attention_distance(proj, kc, vc, st, table, max_pages, page, slopes, None, out, H, G, D, V, window, scale, tiled)
+        both[tiled] = out.cpu()
+    o = 0
+    for s in range(4):
+        one = _Step([new[s]], [prefix[s]], [slots[s]])
+        alone = torch.empty(new[s], H * V, device="cuda")
+        ops.attention_distance(_dev(rows[s][prefix[s]:]), kc, vc, one, table, max_pages, page, slopes, None, alone, H, G, D, V,
+                               window, scale, False)
+        assert torch.equal(both[False][o:o + new[s]], alone.cpu()), s
+        assert (both[True][o:o + new[s]] - alone.cpu()).abs().max() < 2e-5, s
+        full = rows[s].double()
+        want = _plain_attention(full[prefix[s]:, :H * D].reshape(-1, H, D), full[:, H * D:H * D + G * D].reshape(-1, G, D),
+                                full[:, H * D + G * D:].reshape(-1, G, V), None, slopes.double().cpu(), scale, window, prefix[s])
+        assert (alone.double().cpu().view(-1, H, V) - want).abs().max() < 2e-5, s
+        o += new[s]
+
+
+def _router_case(g, T, W, experts, identity, top, groups, keep, shared):
+    n = experts + identity
+    cfg = {"experts": experts, "identity": identity, "top": top}
+    if groups:
+        cfg["groups"] = {"count": groups, "keep": keep}
+    Wt = {"m.router": torch.randn(n, W, generator=g) * (2.5 / W ** 0.5), "m.correction": torch.randn(n, generator=g) * 0.08}
+    for e in range(experts):
+        Wt[f"m.e{e}.gate"] = torch.randn(shared[0], W, generator=g) / W ** 0.5
+        Wt[f"m.e{e}.up"] = torch.randn(shared[0], W, generator=g) / W ** 0.5
+        Wt[f"m.e{e}.down"] = torch.randn(W, shared[0], generator=g) / shared[0] ** 0.5
+    Wt["m.shared.sg"] = torch.randn(1, W, generator=g) * (2.0 / W ** 0.5)
+    return cfg, Wt
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,identity,top,groups,keep", [(6, 2, 3, 4, 2), (5, 0, 1, 0, 0), (1, 3, 2, 0, 0), (12, 4, 4, 4, 3),
+                                                              (16, 0, 6, 8, 8), (0, 4, 2, 2, 1), (40, 8, 8, 6, 2)])
+def test_router_and_experts_both_ways(dtype, experts, identity, top, groups, keep):
+    """The router's choice (correction, groups, identity experts, ties aside) and weights against the plain statement;
+    the chosen experts token by token and expert by expert give the plain result; the shared gate's number per token."""
+    from mdma_b200 import ops
+    g = torch.Generator().manual_seed(experts * 7 + top)
+    T, W, ff = 77, 40, 24
+    cfg, Wt = _router_case(g, T, W, experts, identity, top, groups, keep, (ff,))
+    Wt = {k: v.to(dtype) for k, v in Wt.items()}
+    h = torch.randn(T, W, generator=g).to(dtype)
+    W64 = {k: v.double() for k, v in Wt.items()}
+    chosen_ref, weight_ref, s = pm.route(h.double(), W64, "m.", cfg)
+    n = experts + identity
+    chosen = torch.full((T, top), -7, dtype=torch.int32, device="cuda")
+    weight = torch.empty(T, top, device="cuda")
+    scale = torch.empty(T, device="cuda")
+    ops.route(_dev(h, dtype), _dev(Wt["m.router"], dtype), _dev(Wt["m.correction"], dtype), _dev(Wt["m.shared.sg"].reshape(-1), dtype),
+              T, top, max(groups, 1), max(keep, 1), chosen, weight, scale)
+    assert (scale.double().cpu() - torch.sigmoid(h.double() @ W64["m.shared.sg"].T).view(-1)).abs().max() < 1e-5
+    # a choice may differ from the plain one only where two choice scores are within float rounding of each other
+    c = s + W64["m.correction"]
+    same = 0
+    for t in range(T):
+        mine, ref = set(chosen[t].tolist()), set(chosen_ref[t].tolist())
+        if mine == ref:
+            same += 1
+            order = {e: j for j, e in enumerate(chosen[t].tolist())}
+            for j, e in enumerate(chosen_ref[t].tolist()):
+                assert abs(float(weight[t, order[e]]) - float(weight_ref[t, j])) < 1e-5
+        else:
+            assert all(min(abs(float(c[t, a] - c[t, b])) for b in ref - mine) < 1e-6 for a in mine - ref), t
+    assert same >= T - 1
+    assert abs(float(weight.sum()) - T) < 1e-3
+    if identity:
+        assert (chosen >= experts).any()
+    stack = lambda part: (_dev(torch.cat([Wt[f"m.e{e}.{part}"] for e in range(experts)]), dtype) if experts else None)
+    want = torch.zeros(T, W, dtype=torch.float64)
+    for t in range(T):
+        for j in range(top):
+            e = int(chosen[t, j])
+            y = h[t].double() if e >= experts else pm.gated_ffn(h[t:t + 1].double(), W64, f"m.e{e}.")[0]
+            want[t] += float(weight[t, j]) * y
+    x0 = torch.randn(T, W, generator=g)
+    for way in ("token", "expert"):
+        x = _dev(x0)
+        act = torch.empty(T * top, ff, device="cuda", dtype=dtype)
+        scratch = None
+        if way == "expert":
+            scratch = (torch.full((experts + 1,), -1, dtype=torch.int32, device="cuda"),
+                       torch.full((T * top,), -1, dtype=torch.int32, device="cuda"),
+                       torch.full((T * top * W,), float("nan"), device="cuda"))
+        ops.experts(_dev(h, dtype), stack("gate"), stack("up"), stack("down"), chosen, weight, T, experts, top, ff, act, x, scratch)
+        tol = 2e-5 if dtype == torch.float32 else 3e-2
+        assert (x.double().cpu() - x0.double() - want).abs().max() < tol, way
+
+
+# =====================================================================================================
+# Whole models through the engine (GPU).
+
+_models: dict = {}
+
+
+def model_of(key, dtype):
+    """(folder, config, float64-ready tensors as the engine holds them) of configuration `key`."""
+    k = (key, dtype)
+    if k not in _models:
+        store = torch.float32 if dtype == "float32" else torch.bfloat16
+        d, W = make_model(CONFIGS[key], 11 + ord(key), store)
+        _models[k] = (d, CONFIGS[key], W)
+    return _models[k]
+
+
+_refs: dict = {}
+
+
+def ref_of(key, dtype, ids):
+    k = (key, dtype, tuple(ids))
+    if k not in _refs:
+        _, cfg, W = model_of(key, dtype)
+        _refs[k] = pm.forward(cfg, W, ids).numpy()
+    return _refs[k]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D", "E"])
+def test_every_layer_against_the_plain_statement(key, dtype):
+    """The residual stream after every run of a layer, then the logits; one short prompt."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of(key, dtype)
+    ids = ids_of(cfg, 21, 4)
+    trace = []
+    ref = pm.forward(cfg, W, ids, trace)
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=64, logit_rows=64, page_size=16)
+    got = []
+    eng.model.on_layer = lambda n, x: got.append(x.detach().double().cpu())
+    s = eng.acquire()
+    logits = eng.step([StepEntry(s, ids, list(range(len(ids))))]).cpu().numpy()
+    assert len(got) == len(trace)
+    tol = 1e-4 if dtype == "float32" else 0.03
+    off = set()          # bfloat16: rows where a router's close call fell the other way stay off from then on (see `close`)
+    for n, (a, b) in enumerate(zip(got, trace)):
+        row_err = (a - b).abs().max(dim=-1).values
+        bad = set(torch.nonzero(row_err >= tol * max(1.0, float(b.abs().max()))).view(-1).tolist())
+        assert dtype != "float32" or not bad, f"after run {n} of the schedule"
+        assert len(bad - off) <= 1 and len(bad) <= 3, f"after run {n} of the schedule: rows {sorted(bad)} are off"
+        off |= bad
+    close(logits, ref.numpy(), dtype, "logits")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D", "E"])
+def test_batches_portions_decoding_and_reuse(key, dtype):
+    """Unequal prompts in one step; the same prompts cut in portions down to one and two tokens on a cached prefix;
+    token-by-token decoding past every window; sequences that end early while others go on; slots and pages freed and
+    taken again (rows nobody owns hold NaN throughout).  In float32 every way of cutting gives the same bits."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of(key, dtype)
+    lengths = [70, 1, 33, 2, 17]
+    seqs = [ids_of(cfg, n, 20 + i) for i, n in enumerate(lengths)]
+    refs = [ref_of(key, dtype, s) for s in seqs]
+    eng = Engine(d, dtype=dtype, max_batch=5, max_context=96, logit_rows=160, page_size=16)
+
+    def run(plan):
+        """plan: per sequence, the sizes of its portions.  All sequences advance together, one portion a step."""
+        slots = [eng.acquire() for _ in seqs]
+        rows = [[] for _ in seqs]
+        at = [0] * len(seqs)
+        for step in range(max(len(p) for p in plan)):
+            live = [i for i in range(len(seqs)) if step < len(plan[i])]
+            eng.cache.poison_unused()
+            out = eng.step([StepEntry(slots[i], seqs[i][at[i]:at[i] + plan[i][step]], list(range(plan[i][step])))
+                            for i in live]).cpu().numpy()
+            o = 0
+            for i in live:
+                n = plan[i][step]
+                rows[i].append(out[o:o + n].copy())
+                o += n
+                at[i] += n
+                if at[i] == len(seqs[i]):
+                    eng.release(slots[i])           # ends early; its slot and pages go back
+        eng.cache.check()
+        return [np.concatenate(r) for r in rows]
+
+    whole = run([[n] for n in lengths])
+    for i, (got, ref) in enumerate(zip(whole, refs)):
+        close(got, ref, dtype, f"whole prompts, sequence {i}")
+    alone = []
+    for i, s in enumerate(seqs):                    # each alone, in a slot that the batch used
+        slot = eng.acquire()
+        alone.append(eng.step([StepEntry(slot, s, list(range(len(s))))]).cpu().numpy().copy())
+        eng.release(slot)
+    pieces = run([[2, 1, 30, 17, 1, 2, 16, 1], [1], [16, 1, 15, 1], [1, 1], [3, 14]])
+    decoded = run([[25] + [1] * 45, [1], [1] * 33, [2], [16, 1]])
+    for name, other in (("alone", alone), ("portions", pieces), ("decoded", decoded)):
+        for i, (got, ref) in enumerate(zip(other, refs)):
+            close(got, ref, dtype, f"{name}, sequence {i}")
+            if dtype == "float32":
+                assert np.abs(got - whole[i]).max() <= 2e-6, f"{name}, sequence {i}: differs from the whole prompt"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_passes_smaller_than_a_step_and_long_decoding(dtype):
+    """A step run as passes of 7 tokens (cuts inside sequences), then 150 tokens decoded one by one across many page
+    borders and past the windows (whose pages go back on the way), beside a batch mate that ends on the way and whose
+    slot another request takes."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of("A", dtype)
+    long_ids, mate, late = ids_of(cfg, 190, 31), ids_of(cfg, 60, 32), ids_of(cfg, 25, 33)
+    r_long, r_mate, r_late = (ref_of("A", dtype, s) for s in (long_ids, mate, late))
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=192, logit_rows=64, page_size=16, chunk_tokens=7)
+    a, b = eng.acquire(), eng.acquire()
+    out = eng.step([StepEntry(a, long_ids[:40], [0, 39, 6, 7]), StepEntry(b, mate[:41], [40, 13])]).cpu().numpy()
+    assert eng.forward_passes > 10
+    close(out, np.stack([r_long[0], r_long[39], r_long[6], r_long[7], r_mate[40], r_mate[13]]), dtype, "passes")
+    pb = 41
+    for p in range(40, 190):
+        entries = [StepEntry(a, [long_ids[p]], [0])]
+        second = None
+        if pb < len(mate):
+            entries.append(StepEntry(b, [mate[pb]], [0]))
+            second = r_mate[pb]
+            pb += 1
+        elif pb == len(mate):                       # the mate is done: its slot goes to a late request
+            eng.release(b)
+            b = eng.acquire()
+            entries.append(StepEntry(b, late, [len(late) - 1]))
+            second = r_late[-1]
+            pb += 1
+        eng.cache.poison_unused()
+        out = eng.step(entries).cpu().numpy()
+        close(out[0], r_long[p], dtype, f"decoded position {p}")
+        if second is not None:
+            close(out[1], second, dtype, f"batch mate at step {p}")
+    # the windowed groups gave pages back on the way: fewer are held than the sequence is long
+    held = [len(g.seq_pages[a]) for g in eng.cache.groups]
+    assert min(held) <= 3 and max(held) <= 4
+    eng.cache.check()
+
+
+@pytest.mark.gpu
+def test_a_token_far_back_reaches_the_end_through_the_state_and_only_so():
+    """A model of recurrent layers and windowed attention: one early token is changed; the logits 300 positions later
+    move (the recurrent state carries it, slow channels) although every attention window has long passed it.  The
+    engine agrees with the plain statement on both prompts, in portions that cut across the side-by-side walk."""
+    from mdma_b200.engine import Engine, StepEntry
+    d, cfg, W = model_of("A", "float32")
+    ids = ids_of(cfg, 330, 61)
+    other = list(ids)
+    other[5] = (other[5] + 11) % cfg["vocab"]
+    ra, rb = ref_of("A", "float32", ids), ref_of("A", "float32", other)
+    assert np.abs(ra[-1] - rb[-1]).max() > 20 * TOL_F32
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=384, logit_rows=16, page_size=16)
+    s, t = eng.acquire(), eng.acquire()
+    eng.step([StepEntry(s, ids[:300], []), StepEntry(t, other[:280], [])])
+    out = eng.step([StepEntry(s, ids[300:], [29]), StepEntry(t, other[280:], [49])]).cpu().numpy()
+    close(out[0], ra[-1], "float32", "the prompt")
+    close(out[1], rb[-1], "float32", "the prompt with one early token changed")
+
+
+@pytest.mark.gpu
+def test_long_prompts_on_the_serving_kernels():
+    """Prompts long enough for the side-by-side recurrence, the tiled attention and the expert-by-expert products, in
+    bfloat16, two unequal prompts in one step and then decoded; against the plain statement."""
+    from mdma_b200.engine import Engine, StepEntry
+    for key in ("A", "C"):
+        d, cfg, W = model_of(key, "bfloat16")
+        seqs = [ids_of(cfg, 620, 71), ids_of(cfg, 301, 72)]
+        refs = [ref_of(key, "bfloat16", s) for s in seqs]
+        eng = Engine(d, dtype="bfloat16", max_batch=2, max_context=640, logit_rows=64)
+        slots = [eng.acquire(), eng.acquire()]
+        want = [[0, 1, 299, 300, 500, 610], [0, 150, 295]]
+        eng.cache.poison_unused()
+        out = eng.step([StepEntry(slots[0], seqs[0][:611], want[0]), StepEntry(slots[1], seqs[1][:296], want[1])]).cpu().numpy()
+        close(out, np.concatenate([refs[0][want[0]], refs[1][want[1]]]), "bfloat16", f"{key}: prompts")
+        for p in range(5):
+            eng.cache.poison_unused()
+            out = eng.step([StepEntry(slots[0], [seqs[0][611 + p]], [0]), StepEntry(slots[1], [seqs[1][296 + p]], [0])]).cpu().numpy()
+            close(out, np.stack([refs[0][611 + p], refs[1][296 + p]]), "bfloat16", f"{key}: decoded {p}")
+        eng.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("key", ["A", "C"])
+def test_greedy_generation_through_the_scheduler(key):
+    """`Engine.generate`: batches, the decode session's replayed graphs, argmax.  float32 tokens equal the plain
+    statement's greedy continuation; replayed and step-by-step runs give the same tokens in both dtypes."""
+    from mdma_b200.engine import Engine
+    d, cfg, W = model_of(key, "float32")
+    prompts = [ids_of(cfg, n, 40 + n) for n in (9, 30, 3)]
+    want = []
+    for p in prompts:
+        ids = list(p)
+        for _ in range(12):
+            ids.append(int(pm.forward(cfg, W, ids)[-1].argmax()))
+        want.append(ids[len(p):])
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=64)            # three requests, two slots: two batches
+    assert eng.decode_session().graph_safe
+    for graphs in (True, False):
+        outs = eng.generate(prompts, max_tokens=12, use_graphs=graphs)
+        assert [o.tokens for o in outs] == want, graphs
+    d16, _, _ = model_of(key, "bfloat16")
+    eng = Engine(d16, dtype="bfloat16", max_batch=3, max_context=64)
+    a = eng.generate(prompts, max_tokens=12, use_graphs=True)
+    b = eng.generate(prompts, max_tokens=12, use_graphs=False)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
+    sampled = eng.generate(prompts, max_tokens=8, temperature=0.9, top_p=0.9, seed=3)
+    assert all(len(o.tokens) == 8 for o in sampled)
+
+
+@pytest.mark.gpu
+def test_trace_replay_and_command_line(tmp_path):
+    from replay_util import replay
+    d, cfg, W = model_of("B", "float32")
+    a, b = ids_of(cfg, 30, 50), ids_of(cfg, 11, 51)
+    ra, rb = ref_of("B", "float32", a), ref_of("B", "float32", b)
+    steps = [{"entries": [{"id": "a", "tokens": a[:20], "want": [0, 19]}, {"id": "b", "tokens": b[:9], "want": []}], "end": []},
+             {"entries": [{"id": "a", "tokens": [a[20]], "want": [0]}, {"id": "b", "tokens": [b[9]], "want": [0]}], "end": []},
+             {"entries": [{"id": "a", "tokens": [a[21]], "want": []}, {"id": "b", "tokens": [b[10]], "want": [0]}], "end": ["b"]},
+             {"entries": [{"id": "a", "tokens": a[22:], "want": [7]}], "end": ["a"]}]
+    out = replay(d, "float32", steps, 128, cfg["vocab"])
+    close(out[0], np.stack([ra[0], ra[19]]), "float32", "step 0")
+    close(out[1], np.stack([ra[20], rb[9]]), "float32", "step 1")
+    close(out[2], rb[10:11], "float32", "step 2")
+    close(out[3], ra[29:30], "float32", "step 3")
+    from mdma_b200.cli import main
+    assert main(["run", d, " ".join(map(str, a[:5])), "--max-tokens", "4", "--dtype", "float32", "--max-context", "64"]) == 0
+    assert main(["plan", d, "--ctx", "64"]) == 0
+
+
+def random_config(seed):
+    """A configuration drawn from plausible sizes: both mixers in any order, sizes that are and are not multiples of 8
+    and 16, one to sixteen heads in one to as many groups, windows from 1 to beyond the prompt or none, convolutions of
+    one to eight taps, routers with and without groups, identity experts and shared experts, loops anywhere or nowhere."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([32, 40, 48, 64, 96, 128, 160, 256])
+
+    def mixer(kind):
+        if kind == "rglru":
+            blocks = r.choice([1, 2, 3, 4, 8])
+            return {"width": blocks * r.choice([4, 8, 10, 16, 24, 32]), "blocks": blocks, "conv": r.choice([1, 2, 3, 4, 5, 8])}
+        heads = r.choice([1, 2, 3, 4, 6, 8, 12, 16])
+        kv = r.choice([g for g in (1, 2, 3, 4, 6, 8, 12, 16) if heads % g == 0])
+        return {"heads": heads, "kv_heads": kv, "dim": r.choice([8, 16, 24, 32, 48, 64, 80]), "vdim": r.choice([8, 16, 20, 32, 64, 96]),
+                "scale": round(r.uniform(0.05, 0.4), 3), "mask": r.choice([None, {"size": r.choice([1, 2, 5, 16, 33, 64, 100, 400])}])}
+
+    def mlp():
+        if r.random() < 0.2:
+            return None
+        count = r.choice([1, 1, 2, 3, 4])
+        per = r.randint(1, 4)
+        n = count * per
+        identity = r.randint(0, n) if r.random() < 0.6 else 0
+        keep = r.randint(1, count)
+        top = r.randint(1, min(keep * per, 6))
+        router = {"experts": n - identity, "identity": identity, "top": top}
+        if count > 1 or r.random() < 0.3:
+            router["groups"] = {"count": count, "keep": keep}
+        return {"kind": "moe", "expert": {"ff": r.choice([8, 20, 32, 64, 100])}, "router": router,
+                "shared": None if r.random() < 0.3 else {"ff": r.choice([8, 24, 64, 128])}}
+    n = r.randint(2, 5)
+    layers = [{"type": k, "mixer": mixer(k), "mlp": mlp()} for k in (r.choice(["rglru", "attention"]) for _ in range(n))]
+    cfg = {"architecture": "Mogevik", "vocab": r.randint(40, 500), "width": width, "norm": {"eps": r.choice([1e-5, 1e-6])},
+           "embedding": {"scale": round(r.uniform(1.0, 6.0), 2)}, "layers": layers}
+    if r.random() < 0.7:
+        start = r.randint(0, n - 1)
+        cfg["loop"] = {"start": start, "stop": r.randint(start + 1, n), "times": r.randint(1, 3)}
+    return cfg
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(12))
+def test_random_configurations(seed):
+    """Drawn configurations in both engines: two unequal prompts in one step, six tokens decoded, against the plain
+    statement; pages of 16 or 64 rows."""
+    import random
+    from mdma_b200.engine import Engine, StepEntry
+    cfg = random_config(seed)
+    r = random.Random(1000 + seed)
+    lengths = [r.randint(30, 140), r.randint(1, 40)]
+    seqs = [ids_of(cfg, n + 6, 90 + seed + i) for i, n in enumerate(lengths)]
+    for dtype, store in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        d, W = make_model(cfg, 200 + seed, store)
+        refs = [pm.forward(cfg, W, s).numpy() for s in seqs]
+        eng = Engine(d, dtype=dtype, max_batch=2, max_context=192, logit_rows=192, page_size=r.choice([16, 64]))
+        slots = [eng.acquire(), eng.acquire()]
+        eng.cache.poison_unused()
+        out = eng.step([StepEntry(sl, s[:n], list(range(n))) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
+        close(out[:lengths[0]], refs[0][:lengths[0]], dtype, f"{cfg}: first prompt", drawn=True)
+        close(out[lengths[0]:], refs[1][:lengths[1]], dtype, f"{cfg}: second prompt", drawn=True)
+        for p in range(6):
+            eng.cache.poison_unused()
+            out = eng.step([StepEntry(sl, [s[n + p]], [0]) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
+            close(out, np.stack([refs[0][lengths[0] + p], refs[1][lengths[1] + p]]), dtype, f"{cfg}: decoded {p}", drawn=True)
+        eng.check_status()
+        del eng
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_plan_is_what_is_held_and_generation_takes_nothing_more(dtype):
+    """The memory plan made from sizes alone is what the engine holds, category by category and by the allocator's
+    count; generation, sampled or not, takes nothing more."""
+    import gc
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.step import plan_only
+    d, cfg, W = model_of("A", dtype)
+    gc.collect()
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    eng = Engine(d, dtype=dtype, max_batch=3, max_context=128)
+    held = eng.held_bytes()
+    assert eng.plan["total_bytes"] == held["total_bytes"] == sum(v for k, v in held.items() if k != "total_bytes")
+    for key, value in held.items():
+        assert eng.plan[key] == value, (key, eng.plan[key], value)
+    taken = torch.cuda.memory_allocated() - before
+    assert 0 <= taken - eng.plan["total_bytes"] < (2 << 20), (taken, eng.plan["total_bytes"])
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert plan_only(d, dtype=dtype, max_batch=3, max_context=128, sms=sms) == eng.plan
+    prompts = [ids_of(cfg, n, 80 + n) for n in (5, 40, 17)]
+    eng.generate(prompts, max_tokens=20)                    # warm: kernels loaded, graphs captured
+    eng.generate(prompts, max_tokens=20, temperature=0.7, seed=3)
+    torch.cuda.synchronize()
+    warm = torch.cuda.memory_allocated()
+    for seed2 in range(3):
+        outs = eng.generate(prompts, max_tokens=30, temperature=0.9, top_p=0.9, seed=seed2)
+        assert all(len(o.tokens) == 30 for o in outs)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == warm
+    eng.cache.check()
