@@ -51,6 +51,20 @@ int mdma_attention_mma_sink(const void* q, int q_stride, const void* k_cache, co
                                 nullptr, sink_log2);
 }
 
+// The same with a penalty on distance (and optionally a sink): `slope_log2` [n_heads] floats, the slopes times
+// log2(e); slope_log2[head] * (query position - key position) is taken off every score.
+int mdma_attention_mma_distance(const void* q, int q_stride, const void* k_cache, const void* v_cache, int n_pages,
+                                const int* seq_start, const int* seq_pos0, const int* seq_slot, const int* page_table,
+                                int max_pages, int page_size, void* out, int n_tokens, int n_seqs, int max_new,
+                                int n_heads, int n_kv_heads, int head_dim, int window, float scale, int splits,
+                                float* scratch, long scratch_floats, int* status, const float* sink_log2,
+                                const float* slope_log2, cudaStream_t stream) {
+    return launch_attention_mma(q, q_stride, k_cache, v_cache, seq_start, seq_pos0, seq_slot, page_table,
+                                max_pages, page_size, out, n_tokens, n_seqs, max_new, n_heads, n_kv_heads,
+                                head_dim, window, scale, splits, scratch, scratch_floats, stream, n_pages, status,
+                                nullptr, sink_log2, slope_log2);
+}
+
 // One token per sequence with the rotary encoding and the cache write inside the attention kernel:
 // `qkv` holds the step's projection rows, not rotated; with `proj_splits` > 0 the rows are instead the sums
 // of that many float partial rows at `proj_partial` (`proj_split_stride` floats apart).  The kernel writes

@@ -65,6 +65,9 @@ struct AttnParams {
     // A softmax with a sink: 2^(sink_log2[head] - m) is added to every row's denominator once (a term with
     // no key and no value; the entries are the learned numbers times log2(e)).  Null: an ordinary softmax.
     const float* sink_log2;
+    // A penalty on distance: slope_log2[head] * (query position - key position) is taken off every score
+    // (the entries are the slopes times log2(e)).  Null: none.
+    const float* slope_log2;
     // Decode with the rotary encoding done here (`rot_inv_freq` not null): the step's projection rows are
     // `q` (bfloat16, not yet rotated) or, with `proj_splits` > 0, the sum of that many float partial rows
     // [split][token][proj_width]; the block rotates its query heads and its key head, rounds them to
@@ -144,6 +147,7 @@ attention_mma_kernel(const AttnParams p) {
     const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = pos0 + min(r_lo / G, n_tok - 1), pos_hi = pos0 + min(r_hi / G, n_tok - 1);
     const int win_lo = p.window > 0 ? pos_lo + 1 - p.window : 0, win_hi = p.window > 0 ? pos_hi + 1 - p.window : 0;
+    const float sl_lo = p.slope_log2 ? p.slope_log2[kvh * G + r_lo % G] : 0.f, sl_hi = p.slope_log2 ? p.slope_log2[kvh * G + r_hi % G] : 0.f;
 
     float o[DMAX / 8][4];
 #pragma unroll
@@ -185,8 +189,8 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key_base + n * 8 + e;
-                const float v_lo = (key <= pos_lo && key >= win_lo) ? s[n][e] * p.scale_log2 : -INFINITY;
-                const float v_hi = (key <= pos_hi && key >= win_hi) ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                const float v_lo = (key <= pos_lo && key >= win_lo) ? s[n][e] * p.scale_log2 - sl_lo * (float)(pos_lo - key) : -INFINITY;
+                const float v_hi = (key <= pos_hi && key >= win_hi) ? s[n][2 + e] * p.scale_log2 - sl_hi * (float)(pos_hi - key) : -INFINITY;
                 s[n][e] = v_lo; s[n][2 + e] = v_hi;
                 mx_lo = fmaxf(mx_lo, v_lo); mx_hi = fmaxf(mx_hi, v_hi);
             }
@@ -344,6 +348,9 @@ attention_decode_kernel(const AttnParams p) {
         ldmatrix_x4(sQ + tile_offset<DMAX>(lane & 15, kd * 2 + (lane >> 4)), qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3]);
 
     const int win = p.window > 0 ? pos + 1 - p.window : 0;
+    // rows of the tile are the group's query heads: lane / 4 and that + 8
+    const float sl_lo = p.slope_log2 ? p.slope_log2[kvh * G + min(lane >> 2, G - 1)] : 0.f;
+    const float sl_hi = p.slope_log2 ? p.slope_log2[kvh * G + min((lane >> 2) + 8, G - 1)] : 0.f;
     float o[DMAX / 8][4];
 #pragma unroll
     for (int n = 0; n < DMAX / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
@@ -380,8 +387,8 @@ attention_decode_kernel(const AttnParams p) {
             for (int e = 0; e < 2; ++e) {
                 const int key = key_base + n * 8 + e;
                 const bool vis = key <= pos && key >= win;
-                const float v_lo = vis ? s[n][e] * p.scale_log2 : -INFINITY;
-                const float v_hi = vis ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                const float v_lo = vis ? s[n][e] * p.scale_log2 - sl_lo * (float)(pos - key) : -INFINITY;
+                const float v_hi = vis ? s[n][2 + e] * p.scale_log2 - sl_hi * (float)(pos - key) : -INFINITY;
                 s[n][e] = v_lo; s[n][2 + e] = v_hi;
                 mx_lo = fmaxf(mx_lo, v_lo); mx_hi = fmaxf(mx_hi, v_hi);
             }
@@ -626,6 +633,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         ldmatrix_x4(sQ + tile_offset<DMAX>(lane & 15, kd * 2 + (lane >> 4)), qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3]);
 
     const int win = p.window > 0 ? pos + 1 - p.window : 0;
+    // rows of the tile are the group's query heads: lane / 4 and that + 8
+    const float sl_lo = p.slope_log2 ? p.slope_log2[kvh * G + min(lane >> 2, G - 1)] : 0.f;
+    const float sl_hi = p.slope_log2 ? p.slope_log2[kvh * G + min((lane >> 2) + 8, G - 1)] : 0.f;
     float o[DMAX / 8][4];
 #pragma unroll
     for (int n = 0; n < DMAX / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
@@ -666,8 +676,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             for (int e = 0; e < 2; ++e) {
                 const int key = key_base + n * 8 + e;
                 const bool vis = key <= pos && key >= win;
-                const float v_lo = vis ? s[n][e] * p.scale_log2 : -INFINITY;
-                const float v_hi = vis ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                const float v_lo = vis ? s[n][e] * p.scale_log2 - sl_lo * (float)(pos - key) : -INFINITY;
+                const float v_hi = vis ? s[n][2 + e] * p.scale_log2 - sl_hi * (float)(pos - key) : -INFINITY;
                 s[n][e] = v_lo; s[n][2 + e] = v_hi;
                 mx_lo = fmaxf(mx_lo, v_lo); mx_hi = fmaxf(mx_hi, v_hi);
             }
@@ -863,7 +873,8 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
                        int max_pages, int page_size, void* out, int n_tokens, int n_seqs, int max_new,
                        int n_heads, int n_kv_heads, int head_dim, int window, float scale, int splits,
                        float* scratch, long scratch_floats, cudaStream_t stream, int n_pages = 0,
-                       int* status = nullptr, const FusedRotary* fz = nullptr, const float* sink_log2 = nullptr) {
+                       int* status = nullptr, const FusedRotary* fz = nullptr, const float* sink_log2 = nullptr,
+                       const float* slope_log2 = nullptr) {
     MDMA_REQUIRE(attention_mma_supported(n_heads, n_kv_heads, head_dim),
                  "attention_mma: heads %d / kv heads %d / head_dim %d is outside its limits (head_dim a multiple of 16 up to 128, group up to 64)",
                  n_heads, n_kv_heads, head_dim);
@@ -881,7 +892,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.group = n_heads / n_kv_heads; p.tile_tokens = kRows / p.group; p.window = window; p.splits = splits;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_o = nullptr; p.part_ml = nullptr; p.status = status; p.sink_log2 = sink_log2;
+    p.part_o = nullptr; p.part_ml = nullptr; p.status = status; p.sink_log2 = sink_log2; p.slope_log2 = slope_log2;
     p.rot_inv_freq = nullptr; p.rotary_dim = 0; p.rot_interleaved = 0;
     p.proj_partial = nullptr; p.proj_splits = 0; p.proj_split_stride = 0; p.proj_width = 0;
     p.k_cache_w = nullptr; p.v_cache_w = nullptr;

@@ -42,6 +42,7 @@ struct AttnTcParams {
     float scale_log2;
     int* status;
     const float* sink_log2;       // [n_heads] or null: 2^(sink_log2[head] - reference) joins the row's denominator once
+    const float* slope_log2;      // [n_heads] or null: slope_log2[head] * (query position - key position) is taken off every score
 };
 
 // shared memory map (bytes), all tiles 1024-aligned:
@@ -210,6 +211,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const bool row_valid = t < n_tok;
         const int pos = pos0 + (row_valid ? t : n_tok - 1);
         const int win = p.window > 0 ? pos + 1 - p.window : 0;
+        // the penalty on distance in the units of the raw scores (they are multiplied by scale_log2 later)
+        const float slope_raw = p.slope_log2 != nullptr ? p.slope_log2[kvh * G + g] / p.scale_log2 : 0.f;
         float m_ref = -INFINITY, l = 0.f;                     // reference maximum (log2 domain), this half's running sum
         uint8_t* p_row = base_ptr + kSmemP + (size_t)r * 128;
         // The reference maximum need not be the exact maximum (it lags by up to 2^8 anyway), only the same
@@ -235,6 +238,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             ptx::tc_fence_before_sync();
             if (i & 1) ptx::mbar_arrive(s_read);              // both blocks of the pair are in registers: S may be overwritten
             const int key0 = (b0 + i) * kTcKeys + half * 32;
+            if (slope_raw != 0.f) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sv[j] -= slope_raw * (float)(pos - (key0 + j));
+            }
             const bool need_mask = key0 + 31 > pos || key0 < win;
             if (need_mask) {
 #pragma unroll
@@ -415,7 +422,7 @@ static int attention_tc_run(const void* q, int q_stride, int q_rows_cap, const v
                       int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_slot,
                       const int* page_table, int max_pages, int page_size, void* out, int n_tokens, int n_seqs,
                       int max_new, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                      int* status, const float* sink_log2, cudaStream_t stream) {
+                      int* status, const float* sink_log2, cudaStream_t stream, const float* slope_log2 = nullptr) {
     MDMA_REQUIRE(mdma_attention_tc_supported(n_heads, n_kv_heads, head_dim, page_size),
                  "attention_tc: heads %d / kv heads %d / head_dim %d / page %d is outside its limits", n_heads, n_kv_heads, head_dim, page_size);
     MDMA_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_tc: query rows must be 16-byte aligned");
@@ -428,7 +435,7 @@ static int attention_tc_run(const void* q, int q_stride, int q_rows_cap, const v
     p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
     p.out = (__nv_bfloat16*)out; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.group = G; p.tile_tokens = kTcRows / G; p.window = window; p.n_tokens = n_tokens;
-    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.sink_log2 = sink_log2;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.sink_log2 = sink_log2; p.slope_log2 = slope_log2;
     CUtensorMap mq, mk, mv;
     {   // queries: [tokens][heads][head_dim] inside rows of q_stride elements; box = 64 x G x tile_tokens
         const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)n_heads, (uint64_t)n_tokens, 1};
@@ -475,6 +482,17 @@ int mdma_attention_tc_sink(const void* q, int q_stride, int q_rows_cap, const vo
     return attention_tc_run(q, q_stride, q_rows_cap, k_cache, v_cache, n_pages, seq_start, seq_pos0, seq_slot, page_table,
                             max_pages, page_size, out, n_tokens, n_seqs, max_new, n_heads, n_kv_heads, head_dim, window,
                             scale, status, sink_log2, stream);
+}
+
+// The same with a penalty on distance (and optionally a sink; see AttnTcParams::slope_log2).
+int mdma_attention_tc_distance(const void* q, int q_stride, int q_rows_cap, const void* k_cache, const void* v_cache,
+                               int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_slot,
+                               const int* page_table, int max_pages, int page_size, void* out, int n_tokens, int n_seqs,
+                               int max_new, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                               int* status, const float* sink_log2, const float* slope_log2, cudaStream_t stream) {
+    return attention_tc_run(q, q_stride, q_rows_cap, k_cache, v_cache, n_pages, seq_start, seq_pos0, seq_slot, page_table,
+                            max_pages, page_size, out, n_tokens, n_seqs, max_new, n_heads, n_kv_heads, head_dim, window,
+                            scale, status, sink_log2, stream, slope_log2);
 }
 
 }  // extern "C"

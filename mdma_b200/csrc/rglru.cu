@@ -1,6 +1,6 @@
 // The real-gated linear recurrent unit, and the small row kernels of the layers around it:
-// a layer norm with a weight and no bias, the re-entry of a looped stack by addition, and a
-// per-row scale.
+// a layer norm with a weight and no bias, the re-entry of a looped stack by addition, a
+// per-row scale and an element-wise sigmoid gate.
 //
 // The recurrence, per channel c of a sequence, row by row:
 //     r = sigmoid(rp + rb[c]),  i = sigmoid(ip + ib[c])          (rp, ip: the gates' block-diagonal products)
@@ -176,6 +176,19 @@ scale_rows_kernel(T* __restrict__ v, const float* __restrict__ s, int width) {
         row[e] = from_float<T>(to_float(row[e]) * f);
 }
 
+// ---------------------------------------------------------------- v[t,:] *= sigmoid(g[t,:])
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(T* __restrict__ v, const T* __restrict__ g, int g_stride, int width) {
+    chain_release();
+    chain_wait();
+    const int t = blockIdx.x;
+    T* row = v + (size_t)t * width;
+    const T* gate = g + (size_t)t * g_stride;
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x)
+        row[e] = from_float<T>(to_float(row[e]) / (1.0f + expf(-to_float(gate[e]))));
+}
+
 }  // namespace mdma
 
 using namespace mdma;
@@ -235,6 +248,17 @@ int mdma_scale_rows(void* v, int dtype, const float* s, int n_rows, int width, c
     MDMA_DISPATCH_DTYPE(dtype, T,
         launch_chained(scale_rows_kernel<T>, dim3(n_rows, parts > 64 ? 64 : parts), dim3(256), 0, stream, (T*)v, s, width));
     MDMA_LAUNCH_OK("scale_rows");
+    return 0;
+}
+
+int mdma_sigmoid_gate(void* v, const void* g, int dtype, int g_stride, int n_rows, int width, cudaStream_t stream) {
+    MDMA_REQUIRE(n_rows >= 0 && width > 0 && g_stride >= width, "sigmoid_gate: bad sizes");
+    if (n_rows == 0) return 0;
+    const int parts = (width + 255) / 256;
+    MDMA_DISPATCH_DTYPE(dtype, T,
+        launch_chained(sigmoid_gate_kernel<T>, dim3(n_rows, parts > 64 ? 64 : parts), dim3(256), 0, stream, (T*)v, (const T*)g,
+                       g_stride, width));
+    MDMA_LAUNCH_OK("sigmoid_gate");
     return 0;
 }
 

@@ -477,6 +477,13 @@ def scale_rows(v: torch.Tensor, s: torch.Tensor, n_rows: int) -> None:
     _call("core", "mdma_scale_rows", _ptr(v), _i(dtype_code(v.dtype)), _ptr(s), _i(n_rows), _i(v.shape[1]), _stream())
 
 
+def sigmoid_gate(v: torch.Tensor, g: torch.Tensor, n_rows: int) -> None:
+    """v[t, :] *= sigmoid(g[t, :]) in place; g may be a view of wider rows."""
+    _need_cuda(v, g)
+    assert v.is_contiguous() and g.dtype == v.dtype and g.stride(1) == 1 and g.shape[1] >= v.shape[1]
+    _call("core", "mdma_sigmoid_gate", _ptr(v), _ptr(g), _i(dtype_code(v.dtype)), _i(g.stride(0)), _i(n_rows), _i(v.shape[1]), _stream())
+
+
 def rglru_scan(gates_r, gates_i, u, y, rb, ib, lam, decay: float, seq_start, seq_slot, state, out, n_seqs: int,
                width: int, runs: bool = False) -> None:
     """The real-gated linear recurrence over each sequence's rows: gates_r, gates_i, u [T, width] floats (the

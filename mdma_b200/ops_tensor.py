@@ -259,12 +259,18 @@ def attention_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int, page_si
 
 def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
               window: int, scale: float, splits: Optional[int] = None, impl: Optional[str] = None,
-              st: Optional[TensorState] = None, sink_log2: Optional[torch.Tensor] = None) -> None:
+              st: Optional[TensorState] = None, sink_log2: Optional[torch.Tensor] = None,
+              slope_log2: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache (bfloat16).
     Steps that bring many tokens per sequence run on the tcgen05 kernel, single tokens on the
     decode kernel, what is between (or outside the tcgen05 kernel's limits) on the mma.sync kernel;
     `impl` ("tc" or "mma") forces one.  `sink_log2` [n_heads] floats: a softmax with a sink, the learned
-    numbers times log2(e); each joins its head's denominators once, with no key and no value."""
+    numbers times log2(e); each joins its head's denominators once, with no key and no value.
+    `slope_log2` [n_heads] floats: a penalty on distance, the slopes times log2(e); slope * (query position -
+    key position) is taken off every score."""
+    if slope_log2 is not None:
+        _need_cuda(slope_log2)
+        assert slope_log2.dtype == torch.float32 and slope_log2.is_contiguous() and slope_log2.numel() == n_heads
     if sink_log2 is not None:
         _need_cuda(sink_log2)
         assert sink_log2.dtype == torch.float32 and sink_log2.is_contiguous() and sink_log2.numel() == n_heads
@@ -287,7 +293,9 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
                 _ptr(view.page_table), _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens),
                 _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale),
                 _ptr(st.status))
-        if sink_log2 is None:
+        if slope_log2 is not None:
+            _call("tensor", "mdma_attention_tc_distance", *args, _ptr(sink_log2), _ptr(slope_log2), _stream())
+        elif sink_log2 is None:
             _call("tensor", "mdma_attention_tc", *args, _stream())
         else:
             _call("tensor", "mdma_attention_tc_sink", *args, _ptr(sink_log2), _stream())
@@ -307,7 +315,10 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
             _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs),
             _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
             _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status))
-    if sink_log2 is None:
+    if slope_log2 is not None:
+        _call("tensor", "mdma_attention_mma_distance", *args, _ptr(sink_log2), _ptr(slope_log2), _stream(),
+              launches=2 if splits > 1 else 1)
+    elif sink_log2 is None:
         _call("tensor", "mdma_attention_mma_paged", *args, _stream(), launches=2 if splits > 1 else 1)
     else:
         _call("tensor", "mdma_attention_mma_sink", *args, _ptr(sink_log2), _stream(), launches=2 if splits > 1 else 1)

@@ -12,10 +12,14 @@ multiplied element by element with sigmoid(Wg h) before the output product; the 
 added to the residual stream.  Heads, sizes, scale, window and the slopes' power are parameters
 (`slope_power` 0: no penalty).
 
-Keys and values go to the paged cache as they leave the projection.  Steps that bring many tokens per
-sequence run on a kernel that stages a tile's keys and values in shared memory; single tokens, the
-32-bit engine and geometries whose tile does not fit run on the kernel that keeps a warp per (token,
-head) and visits keys in position order.
+Keys and values go to the paged cache as they leave the projection.  In the serving engine, heads whose
+keys and values have one size that the tensor-core attention kernels take run on those (the tcgen05
+kernel for long steps, the mma.sync kernel between, the decode kernel for single tokens: the same
+kernels as the other attention mixers, with the slopes as one more per-head parameter); the gate is
+then a small kernel of its own.  Other geometries run on this mixer's CUDA-core kernels, which take
+keys and values of different sizes and apply the gate themselves: one that stages a tile's keys and
+values in shared memory for steps of many tokens, and one that keeps a warp per (token, head) and
+visits keys in position order (single tokens, and everything in the 32-bit engine).
 """
 from __future__ import annotations
 
@@ -78,7 +82,7 @@ class DistanceAttention(Part):
         return fused
 
     def device_tensors(self):
-        return {"slopes": ((self.n_heads,), torch.float32)}
+        return {"slopes": ((self.n_heads,), torch.float32), "slopes_log2": ((self.n_heads,), torch.float32)}
 
     def kv_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window, v_dim=0 if self.v_dim == self.head_dim else self.v_dim)
@@ -112,6 +116,13 @@ class DistanceAttention(Part):
         self.g = Linear(tensors["g"], rt) if self.gate else None
         self.o = Linear(tensors["o"], rt)
         self.slopes = rt.derived(self.slope_values())
+        self.slopes_log2 = None
+        self._fast_ok = False
+        if rt.attention == "fast" and self.v_dim == self.head_dim:
+            from .. import ops_tensor
+            self._fast_ok = ops_tensor.attention_supported(self.n_heads, self.n_kv_heads, self.head_dim)
+        if self._fast_ok:
+            self.slopes_log2 = rt.derived((self.slope_values().double() * 1.4426950408889634).to(torch.float32))
         self._tiled_ok = ops.attention_distance_tiled_fits(self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim)
 
     def forward(self, ctx, h, x, view, owns_cache=True):
@@ -127,6 +138,14 @@ class DistanceAttention(Part):
         if owns_cache:
             ops.kv_store(qkv, self.q_width, self.q_width + self.k_width, self.k_width, self.v_width, ctx.tok_seq,
                          ctx.tok_pos, ctx.seq_slot, view.page_table, view.max_pages, view.page_size, view.k, view.v, n)
+        if self._fast_ok:
+            from .. import ops_tensor
+            ops_tensor.attention(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale,
+                                 st=self.rt.tc, slope_log2=self.slopes_log2)
+            if gate is not None:
+                ops.sigmoid_gate(out, gate, n)
+            self.o.accumulate(out, x, n, defer=False)
+            return
         tiled = self._tiled_ok and ctx.max_new >= self.TILED_FROM and qkv.dtype != torch.float32
         ops.attention_distance(qkv, view.k, view.v, ctx, view.page_table, view.max_pages, view.page_size, self.slopes,
                                gate, out, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, self.window,

@@ -58,7 +58,7 @@ CFG_C = {
     "layers": [
         _layer("attention", _attn(8, 2, 32, 64, 0.18, 64), _moe(64, 8, 4, identity=8, groups=(4, 3), shared=96)),
         _layer("rglru", {"width": 192, "blocks": 4, "conv": 4}, _moe(48, 1, 2, identity=3, shared=32)),
-        _layer("attention", _attn(2, 2, 64, 16, 0.12, 150), _moe(80, 16, 6, groups=(8, 4))),
+        _layer("attention", _attn(2, 2, 64, 64, 0.12, 150), _moe(80, 16, 6, groups=(8, 4))),
     ],
 }
 

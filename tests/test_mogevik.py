@@ -413,6 +413,76 @@ def test_attention_batch_of_unequal_sequences_equals_each_alone():
         o += new[s]
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,G,D,window", [(4, 4, 64, 0), (8, 2, 128, 100), (3, 1, 32, 37), (16, 4, 128, 64), (6, 2, 16, 129)])
+@pytest.mark.parametrize("impl", ["tc", "mma", None])
+def test_tensor_core_attention_with_a_distance_penalty(H, G, D, window, impl):
+    """The tensor-core attention kernels with the slopes as a per-head parameter: a prompt in one step (both kernels),
+    a second portion on the cached prefix, then single tokens (the decode kernels, with and without split keys), against
+    the plain statement.  A far key stands out for one query, and the key at the window's edge for the two queries
+    around it; pages are scattered and rows nobody owns hold NaN."""
+    from mdma_b200 import ops, ops_tensor
+    from mdma_b200.cache import KVView
+    from test_gevonex import _Step
+    g = torch.Generator().manual_seed(H * D + window)
+    T, page, scale = 300, 64, 0.2
+    if impl == "tc" and not ops_tensor.attention_tc_supported(H, G, D, page):
+        pytest.skip("outside the tcgen05 kernel's limits")
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float64)
+    k = torch.randn(T, G, D, generator=g).to(torch.bfloat16).double()
+    v = torch.randn(T, G, D, generator=g).to(torch.bfloat16).double()
+    q = torch.randn(T, H, D, generator=g) * 0.5
+    far = 5
+    k[:, :, 0] = 0
+    k[:, :, 1] = 0
+    k[far, 1 // (H // G), 0] = 8.0
+    q[T - 1, 1] = 0
+    q[T - 1, 1, 0] = float((12.0 + slopes[1] * T) / (8.0 * scale))
+    if window:
+        edge = T - 1 - window
+        k[edge, 0, 1] = 8.0
+        q[T - 2, 0] = 0
+        q[T - 2, 0, 1] = float((12.0 + slopes[0] * T) / (8.0 * scale))
+        q[T - 1, 0] = q[T - 2, 0]
+    q = q.to(torch.bfloat16).double()
+    want = _plain_attention(q, k, v, None, slopes, scale, window, 0)
+    n_pages, max_pages = 12, 6
+    perm = torch.randperm(n_pages, generator=g)[:max_pages].to(torch.int32)
+    kc = torch.full((n_pages, page, G, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    vc = torch.full((n_pages, page, G, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    table = torch.zeros(3, max_pages, dtype=torch.int32)
+    table[1] = perm
+    table = table.cuda()
+    view = KVView(kc, vc, table, page, max_pages, window)
+    slope_log2 = (slopes * 1.4426950408889634).float().cuda()
+    proj = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1).to(torch.bfloat16).cuda()
+    out = torch.empty(T, H * D, device="cuda", dtype=torch.bfloat16)
+    at = 0
+    for n in (200, 80):
+        st = _Step([n], [at], [1])
+        ops.kv_store(proj[at:at + n], H * D, H * D + G * D, G * D, G * D, st.tok_seq, st.tok_pos, st.seq_slot, table, max_pages,
+                     page, kc, vc, n)
+        ops_tensor.attention(st, proj[at:at + n], view, out[at:at + n], H, G, D, window, scale, impl=impl, slope_log2=slope_log2)
+        at += n
+    for t in range(at, T):                      # single tokens
+        st = _Step([1], [t], [1])
+        ops.kv_store(proj[t:t + 1], H * D, H * D + G * D, G * D, G * D, st.tok_seq, st.tok_pos, st.seq_slot, table, max_pages,
+                     page, kc, vc, 1)
+        for splits in ((None,) if t % 2 else (1, 3)):
+            ops_tensor.attention(st, proj[t:t + 1], view, out[t:t + 1], H, G, D, window, scale, splits=splits, slope_log2=slope_log2)
+            got = out[t].double().cpu().reshape(H, D)
+            assert (got - want[t]).abs().max() < 4e-2, (t, splits)
+    ops_tensor.check_status(kc.device)
+    got = out.double().cpu().reshape(T, H, D)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 4e-2
+    if not window:
+        assert (want[T - 1, 1] - v[far, 1 // (H // G)]).abs().max() < 0.05 * v[far].abs().max()
+    else:
+        assert (want[T - 2, 0] - v[edge, 0]).abs().max() < 0.05 * v[edge, 0].abs().max()
+        assert (want[T - 1, 0] - v[edge, 0]).abs().max() > 0.2 * v[edge, 0].abs().max()
+
+
 def _router_case(g, T, W, experts, identity, top, groups, keep, shared):
     n = experts + identity
     cfg = {"experts": experts, "identity": identity, "top": top}
