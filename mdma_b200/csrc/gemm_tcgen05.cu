@@ -977,4 +977,71 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     return splitk_reduce_run(mode, scratch, splits, n_tokens, n_features, out, ldo, out_f32, store_act, act, stream);
 }
 
+// Several products of one shape family in one call: run r multiplies rows [first[r], first[r+1]) of x (and writes the
+// same rows of out) with the r-th matrix of a stack (`w_stride` elements apart; w2 likewise for the gated mode).  `first`
+// is read on the host.  Each run is planned and launched as a product of its own.  A run of a few hundred rows fills a
+// small part of the device (eight block pairs of 74 for 1,024 features x 512 rows), so the runs are dealt out to four
+// side streams that fork from `stream` and join it again, and are launched in forms that need no scratch (no even
+// split of the block pairs' last rounds, no K split through global memory): concurrent products share nothing but
+// the status word.  Blocks of two of these kernels never share an SM's tensor memory beyond its 512 columns: a block
+// of the pair kernel takes an SM's shared memory alone, and the one-block kernel takes at most 256 columns a block,
+// two blocks an SM.
+static constexpr int kRunStreams = 4;
+struct RunStreams { int device; cudaStream_t side[kRunStreams]; cudaEvent_t fork, join[kRunStreams]; };
+static RunStreams* run_streams() {
+    static RunStreams rs[16];
+    static bool made[16] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+    if (!made[dev]) {
+        rs[dev].device = dev;
+        for (int i = 0; i < kRunStreams; ++i) {
+            if (cudaStreamCreateWithFlags(&rs[dev].side[i], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+            if (cudaEventCreateWithFlags(&rs[dev].join[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        }
+        if (cudaEventCreateWithFlags(&rs[dev].fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        made[dev] = true;
+    }
+    return &rs[dev];
+}
+
+int mdma_gemm_tc_runs(int mode, const void* x, int ldx, const void* w, const void* w2, long w_stride, void* out,
+                      int out_f32, int ldo, const int* first, int n_runs, int n_features, int K, int sm_count,
+                      float* scratch, long scratch_floats, int* status, int* sk_flags, int act, cudaStream_t stream) {
+    (void)scratch; (void)scratch_floats; (void)sk_flags;
+    MDMA_REQUIRE(n_runs >= 0 && first != nullptr && w_stride >= (long)n_features * K, "gemm_tc_runs: bad run list");
+    MDMA_REQUIRE(mode == kTcStore || mode == kTcSwiGLU, "gemm_tc_runs: stored and gated products only");
+    RunStreams* rs = run_streams();
+    MDMA_REQUIRE(rs != nullptr, "gemm_tc_runs: could not make the side streams");
+    const size_t out_bytes = out_f32 ? 4 : 2;
+    int live = 0;
+    for (int r = 0; r < n_runs; ++r) live += first[r + 1] > first[r];
+    const int lanes = live < kRunStreams ? live : kRunStreams;
+    if (lanes == 0) return 0;
+    if (cudaEventRecord(rs->fork, stream) != cudaSuccess) return fail("gemm_tc_runs: fork failed");
+    for (int i = 0; i < lanes; ++i) cudaStreamWaitEvent(rs->side[i], rs->fork, 0);
+    int rc = 0, at = 0;
+    for (int r = 0; r < n_runs && rc == 0; ++r) {
+        const int lo = first[r], m = first[r + 1] - first[r];
+        if (lo < 0 || m < 0) { rc = fail("gemm_tc_runs: run %d is not a run", r); break; }
+        if (m == 0) continue;
+        int bn = 0, splits = 0;
+        rc = mdma_gemm_tc_plan(mode, m, n_features, K, sm_count, &bn, &splits);
+        if (rc) break;
+        if (splits > 1) splits = 1;          // no partial sums through the scratch: the runs side by side fill the device
+        const char* xr = (const char*)x + (size_t)lo * ldx * 2;
+        const char* wr = (const char*)w + (size_t)r * w_stride * 2;
+        const char* w2r = w2 ? (const char*)w2 + (size_t)r * w_stride * 2 : nullptr;
+        char* outr = (char*)out + (size_t)lo * ldo * out_bytes;
+        rc = mdma_gemm_tc(mode, xr, ldx, wr, w2r, outr, out_f32, ldo, m, n_features, K, bn, splits, nullptr, 0, status, 0,
+                          nullptr, nullptr, nullptr, nullptr, kF32, act, rs->side[at % lanes]);
+        ++at;
+    }
+    for (int i = 0; i < lanes; ++i) {        // joined also after an error: nothing is left running beside the stream
+        cudaEventRecord(rs->join[i], rs->side[i]);
+        cudaStreamWaitEvent(stream, rs->join[i], 0);
+    }
+    return rc;
+}
+
 }  // extern "C"

@@ -25,10 +25,37 @@ namespace mdma {
 
 constexpr int kMaxRouted = 1024, kMaxTop = 32;
 
+// eight consecutive elements as floats, by 16-byte loads (the address must be 16-byte aligned)
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+}
+
+// A warp's dot product over n elements; `vec`: n is a multiple of 8 and both rows start on 16-byte boundaries, so a lane
+// takes eight consecutive elements at a time.  Either way the order of additions is fixed.
 template <typename TA, typename TW>
-__device__ __forceinline__ float warp_dot(const TA* __restrict__ a, const TW* __restrict__ w, int n, int lane) {
+__device__ __forceinline__ float warp_dot(const TA* __restrict__ a, const TW* __restrict__ w, int n, int lane, bool vec = false) {
     float acc = 0.f;
-    for (int k = lane; k < n; k += 32) acc = fmaf(to_float(a[k]), to_float(w[k]), acc);
+    if (vec) {
+        for (int k = lane * 8; k < n; k += 256) {
+            float x[8], y[8];
+            load8(a + k, x);
+            load8(w + k, y);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(x[i], y[i], acc);
+        }
+    } else {
+        for (int k = lane; k < n; k += 32) acc = fmaf(to_float(a[k]), to_float(w[k]), acc);
+    }
     return warp_sum(acc);
 }
 
@@ -117,13 +144,25 @@ expert_gate_up_kernel(const TA* __restrict__ h, int h_stride, const TW* __restri
     for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(row[k]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const bool vec = width % 8 == 0 && (((uintptr_t)G | (uintptr_t)U) & 15) == 0;
     for (int f = blockIdx.y * n_warps + warp; f < ff; f += gridDim.y * n_warps) {
         const TW* g = G + ((size_t)e * ff + f) * width;
         const TW* u = U + ((size_t)e * ff + f) * width;
         float ag = 0.f, au = 0.f;
-        for (int k = lane; k < width; k += 32) {
-            ag = fmaf(hs[k], to_float(g[k]), ag);
-            au = fmaf(hs[k], to_float(u[k]), au);
+        if (vec) {
+            for (int k = lane * 8; k < width; k += 256) {
+                float x[8], a[8], b[8];
+                load8(hs + k, x);
+                load8(g + k, a);
+                load8(u + k, b);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { ag = fmaf(x[i], a[i], ag); au = fmaf(x[i], b[i], au); }
+            }
+        } else {
+            for (int k = lane; k < width; k += 32) {
+                ag = fmaf(hs[k], to_float(g[k]), ag);
+                au = fmaf(hs[k], to_float(u[k]), au);
+            }
         }
         ag = warp_sum(ag);
         au = warp_sum(au);
@@ -141,6 +180,7 @@ expert_down_kernel(const TA* __restrict__ act, const TA* __restrict__ h, int h_s
     chain_wait();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const bool vec = ff % 8 == 0 && (((uintptr_t)D | (uintptr_t)act) & 15) == 0;
     for (int f = blockIdx.y * n_warps + warp; f < width; f += gridDim.y * n_warps) {
         float total = 0.f;
         for (int j = 0; j < top; ++j) {
@@ -148,43 +188,62 @@ expert_down_kernel(const TA* __restrict__ act, const TA* __restrict__ h, int h_s
             if (e < 0) continue;
             const float w = weights[(size_t)t * top + j];
             if (e >= n_experts) { total += w * to_float(h[(size_t)t * h_stride + f]); continue; }
-            total += w * warp_dot(act + ((size_t)t * top + j) * ff, D + ((size_t)e * width + f) * ff, ff, lane);
+            total += w * warp_dot(act + ((size_t)t * top + j) * ff, D + ((size_t)e * width + f) * ff, ff, lane, vec);
         }
         if (lane == 0) x[(size_t)t * width + f] += total;
     }
 }
 
 // ---------------------------------------------------------------- expert by expert
-// counts[e] pairs choose expert e (identity experts are not counted); order[] lists the pairs sorted by expert,
-// pairs of one expert in rising pair number; first[e] is where expert e's run starts (first[n_experts]: the total).
-// One block: the step's pairs are few enough for a serial scan per expert chunk (a thread per expert counts its own).
+// The (token, choice) pairs sorted by expert: first[e] is where expert e's run starts in `order` (first[n_experts]: the
+// total; identity experts are not counted), order[] lists the pairs expert after expert and where[] is its inverse.
+// Three small kernels: every pair adds one to its expert's counter; one block turns the counters into starts (and
+// clears them); every pair takes the next place of its expert's run.  The order inside a run depends on who comes
+// first, the results do not: every pair's row is computed on its own.
 __global__ void __launch_bounds__(256)
-expert_sort_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int* __restrict__ first,
-                   int* __restrict__ order, int* __restrict__ where) {
+expert_count_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int* __restrict__ counters) {
     chain_release();
     chain_wait();
-    __shared__ int counts[kMaxRouted + 1];
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        int n = 0;
-        for (int p = 0; p < n_pairs; ++p) n += chosen[p] == e;
-        counts[e] = n;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < n_experts; ++e) { const int n = counts[e]; counts[e] = run; run += n; }
-        counts[n_experts] = run;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) first[e] = counts[e];
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        int at = counts[e];
-        for (int p = 0; p < n_pairs; ++p)
-            if (chosen[p] == e) {
-                if (where) where[p] = at;          // the inverse: where pair p stands in the sorted list
-                order[at++] = p;
-            }
-    }
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n_pairs) return;
+    const int e = chosen[p];
+    if (e >= 0 && e < n_experts) atomicAdd(&counters[e], 1);
+}
+
+__global__ void __launch_bounds__(32)
+expert_starts_kernel(int n_experts, int* __restrict__ first, int* __restrict__ counters) {
+    chain_release();
+    chain_wait();
+    if (threadIdx.x != 0) return;
+    int run = 0;
+    for (int e = 0; e < n_experts; ++e) { first[e] = run; run += counters[e]; counters[e] = 0; }
+    first[n_experts] = run;
+}
+
+__global__ void __launch_bounds__(256)
+expert_place_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, const int* __restrict__ first,
+                    int* __restrict__ counters, int* __restrict__ order, int* __restrict__ where) {
+    chain_release();
+    chain_wait();
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n_pairs) return;
+    const int e = chosen[p];
+    if (e < 0 || e >= n_experts) return;
+    const int at = first[e] + atomicAdd(&counters[e], 1);
+    order[at] = p;
+    if (where) where[p] = at;
+}
+
+// `first` holds 2 * (n_experts + 1) ints: the starts, then the counters
+static int sort_pairs(const int* chosen, int n_pairs, int n_experts, int* first, int* order, int* where, cudaStream_t stream) {
+    int* counters = first + n_experts + 1;
+    if (cudaMemsetAsync(counters, 0, sizeof(int) * (size_t)(n_experts + 1), stream) != cudaSuccess) return fail("experts: memset failed");
+    const int blocks = (n_pairs + 255) / 256;
+    expert_count_kernel<<<blocks, 256, 0, stream>>>(chosen, n_pairs, n_experts, counters);
+    expert_starts_kernel<<<1, 32, 0, stream>>>(n_experts, first, counters);
+    expert_place_kernel<<<blocks, 256, 0, stream>>>(chosen, n_pairs, n_experts, first, counters, order, where);
+    MDMA_LAUNCH_OK("expert sort");
+    return 0;
 }
 
 // rows[i] = h[order[i] / top] for the sorted pairs i < first[n_experts]: the experts' inputs, expert after expert,
@@ -411,7 +470,7 @@ int mdma_experts_by_token(const void* h, int h_dtype, int h_stride, const void* 
     return 0;
 }
 
-// Expert by expert: first [n_experts + 1] and order [n_tokens * top] ints, act [n_tokens * top, ff] in h's dtype and
+// Expert by expert: first [2 * (n_experts + 1)] and order [n_tokens * top] ints, act [n_tokens * top, ff] in h's dtype and
 // y [n_tokens * top, width] floats are scratch.
 int mdma_experts_sorted(const void* h, int h_dtype, int h_stride, const void* G, const void* U, const void* D,
                         int w_dtype, const int* chosen, const float* weights, int n_tokens, int n_experts, int top,
@@ -424,7 +483,7 @@ int mdma_experts_sorted(const void* h, int h_dtype, int h_stride, const void* G,
     const int wparts = (width + 255) / 256 > 64 ? 64 : (width + 255) / 256;
     MDMA_DISPATCH_2(h_dtype, TA, w_dtype, TW, {
         if (n_experts > 0) {
-            launch_chained(expert_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, n_experts, first, order, (int*)nullptr);
+            if (int rc = sort_pairs(chosen, n_pairs, n_experts, first, order, nullptr, stream)) return rc;
             launch_chained(expert_gate_up_sorted_kernel<TA, TW>, dim3((ff + kFeatTile - 1) / kFeatTile, pair_tiles, n_experts),
                            dim3(256), 0, stream, (const TA*)h, h_stride, (const TW*)G, (const TW*)U, first, order, top, width,
                            ff, (TA*)act);
@@ -447,7 +506,7 @@ int mdma_experts_gather(const void* h, int h_dtype, int h_stride, const int* cho
     if (n_tokens == 0) return 0;
     const int n_pairs = n_tokens * top;
     const int wparts = (width + 255) / 256 > 64 ? 64 : (width + 255) / 256;
-    launch_chained(expert_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, n_experts, first, order, where);
+    if (int rc = sort_pairs(chosen, n_pairs, n_experts, first, order, where, stream)) return rc;
     MDMA_DISPATCH_DTYPE(h_dtype, TA,
         launch_chained(expert_gather_kernel<TA>, dim3(n_pairs, wparts), dim3(256), 0, stream, (const TA*)h, h_stride,
                        (const int*)first, (const int*)order, n_experts, top, width, (TA*)rows));

@@ -557,7 +557,7 @@ def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: 
             sorted_scratch=None) -> None:
     """x += sum over each token's chosen experts of weight * expert(h) (identity experts: weight * h).  gate_w, up_w
     [experts * ff, width], down_w [experts * width, ff]; act [tokens * top, ff] scratch in h's dtype.
-    `sorted_scratch` = (first, order, y): the expert-by-expert kernels (steps of many tokens); else token by token."""
+    `sorted_scratch` = (first [2 * (experts + 1)] ints, order, y): the expert-by-expert kernels (steps of many tokens); else token by token."""
     _need_cuda(h, gate_w, up_w, down_w, chosen, weights, act, x)
     width = h.shape[1]
     assert h.stride(1) == 1 and x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == width
@@ -574,7 +574,7 @@ def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: 
         return
     first, order, y = sorted_scratch
     _need_cuda(first, order, y)
-    assert first.dtype == order.dtype == torch.int32 and first.numel() >= n_experts + 1 and order.numel() >= n_tokens * top
+    assert first.dtype == order.dtype == torch.int32 and first.numel() >= 2 * (n_experts + 1) and order.numel() >= n_tokens * top
     assert y.dtype == torch.float32 and y.is_contiguous() and y.numel() >= n_tokens * top * width
     _call("core", "mdma_experts_sorted", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(gate_w), _ptr(up_w),
           _ptr(down_w), _i(wd), _ptr(chosen), _ptr(weights), _i(n_tokens), _i(n_experts), _i(top), _i(width), _i(ff),
@@ -588,7 +588,7 @@ def experts_gather(h, chosen, n_tokens: int, n_experts: int, top: int, first, or
     width = h.shape[1]
     assert h.stride(1) == 1 and rows.is_contiguous() and rows.dtype == h.dtype and rows.shape[1] == width
     assert first.dtype == order.dtype == where.dtype == chosen.dtype == torch.int32
-    assert first.numel() >= n_experts + 1 and order.numel() >= n_tokens * top and where.numel() >= n_tokens * top
+    assert first.numel() >= 2 * (n_experts + 1) and order.numel() >= n_tokens * top and where.numel() >= n_tokens * top
     assert rows.shape[0] >= n_tokens * top
     _call("core", "mdma_experts_gather", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(chosen), _i(n_tokens),
           _i(n_experts), _i(top), _i(width), _ptr(first), _ptr(order), _ptr(where), _ptr(rows), _stream(), launches=2)

@@ -211,6 +211,35 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
         st.pending = Pending(out, mode, used.value, M, N)
 
 
+def gemm_runs(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first: list, n_features: int,
+              mode: int = ops.GEMM_STORE, w2: Optional[torch.Tensor] = None, st: Optional[TensorState] = None,
+              act: int = ops.ACT_SILU) -> None:
+    """Run r = 0.. of rows: out[first[r]:first[r+1]] = a[first[r]:first[r+1]] @ w[r * n_features:(r+1) * n_features].T
+    (gated mode: act(gate) * up with w2 stacked likewise).  `first`: a host list of len(runs) + 1 row numbers.  One
+    call for all runs: the loop over the products is in the library."""
+    _need_cuda(a, w, out, w2)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core product takes bfloat16 operands")
+    n_runs = len(first) - 1
+    K = w.shape[1]
+    assert a.dim() == 2 and a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous() and a.shape[1] == K
+    assert w.shape[0] == n_runs * n_features and out.shape[1] == n_features and out.shape[0] >= first[-1] <= a.shape[0]
+    assert w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype)
+    st = st or _device_state(a.device)
+    flush_pending(a.device, st)
+    most = max(first[r + 1] - first[r] for r in range(n_runs)) if n_runs else 0
+    if most == 0:
+        return
+    bn, splits = gemm_plan(mode, most, n_features, K, st.sms)
+    st.need(max(gemm_scratch_floats(bn, max(splits, 1), most, n_features, st.sms), 2 * st.sms * 128 * 64), "a K-split product")
+    arr = (ctypes.c_int * (n_runs + 1))(*first)
+    live = sum(1 for r in range(n_runs) if first[r + 1] > first[r])
+    _call("tensor", "mdma_gemm_tc_runs", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), ctypes.c_long(n_features * K),
+          _ptr(out), _i(int(out.dtype == torch.float32)), _i(out.stride(0)), arr, _i(n_runs), _i(n_features), _i(K),
+          _i(st.sms), _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status),
+          _ptr(st.sk_flags) if EVEN_SPLIT else None, _i(act), _stream(), launches=live)
+
+
 def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
     return (n_kv_heads > 0 and n_heads % n_kv_heads == 0 and head_dim % 16 == 0 and 16 <= head_dim <= 128
             and n_heads // n_kv_heads <= 64)

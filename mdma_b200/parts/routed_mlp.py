@@ -80,7 +80,7 @@ class RoutedMLP(Part):
         return {f"experts.{part}": tuple(f"e{e}.{part}" for e in range(self.n_experts)) for part in ("gate", "up", "down")}
 
     def device_tensors(self):
-        return {"first": ((self.n_experts + 1,), torch.int32)}
+        return {"first": ((2 * (self.n_experts + 1),), torch.int32)}          # the experts' starts in the sorted list, and counters
 
     def _names(self):
         tag = f"{self.top}_{self.ff}_{self.hidden}"
@@ -116,13 +116,12 @@ class RoutedMLP(Part):
             self.shared_down = Linear(tensors["shared.down"], rt)
             if self.shared_gate:
                 self.sg = tensors["shared.sg"].reshape(-1)
-        self.first = rt.derived(torch.zeros(self.n_experts + 1, dtype=torch.int32))
-        # a product pair per expert, over views of the stacked matrices (the tensor-core way of long prompts)
-        self.expert_up, self.expert_down = [], []
-        if self.n_experts and rt.gemm == "tensor":
-            F, W = self.ff, self.hidden
-            self.expert_up = [Linear(self.w_gate[e * F:(e + 1) * F], rt, self.w_up[e * F:(e + 1) * F]) for e in range(self.n_experts)]
-            self.expert_down = [Linear(self.w_down[e * W:(e + 1) * W], rt) for e in range(self.n_experts)]
+        self.first = rt.derived(torch.zeros(2 * (self.n_experts + 1), dtype=torch.int32))
+        # long prompts in the serving engine: a tensor-core product pair per expert over its run of gathered rows
+        self.by_products = False
+        if self.n_experts and rt.gemm == "tensor" and self.w_gate.dtype == torch.bfloat16:
+            from .. import ops_tensor
+            self.by_products = (ops_tensor.gemm_supported(self.ff, self.hidden) and ops_tensor.gemm_supported(self.hidden, self.ff))
 
     def forward(self, ctx, h, x):
         n = ctx.n_tokens
@@ -136,7 +135,7 @@ class RoutedMLP(Part):
         scale = ctx.buf(names[6], 1, torch.float32)
         ops.route(h, self.router, self.correction_values, self.sg, n, self.top, self.groups, self.keep_groups, chosen,
                   weight, scale if self.sg is not None else None)
-        if (self.expert_up and n >= self.PRODUCTS_FROM and not getattr(ctx, "decode_only", False)
+        if (self.by_products and n >= self.PRODUCTS_FROM and not getattr(ctx, "decode_only", False)
                 and not torch.cuda.is_current_stream_capturing()):
             self._experts_by_products(ctx, h, x, chosen, weight, act, names)
             self._shared(ctx, h, x, scale)
@@ -158,12 +157,10 @@ class RoutedMLP(Part):
         rows = ctx.buf(names[8], self.top * self.hidden).view(-1, self.hidden)
         act = act.view(-1, self.ff)
         ops.experts_gather(h, chosen, n, self.n_experts, self.top, self.first, order, where, rows)
-        first = self.first.tolist()                          # how many rows each expert got: read on the host
-        for e in range(self.n_experts):
-            lo, m = first[e], first[e + 1] - first[e]
-            if m:
-                self.expert_up[e].gated(rows[lo:lo + m], act[lo:lo + m], m)
-                self.expert_down[e].store(act[lo:lo + m], y[lo:lo + m], m)
+        first = self.first[:self.n_experts + 1].tolist()     # how many rows each expert got: read on the host
+        from .. import ops_tensor
+        ops_tensor.gemm_runs(rows, self.w_gate, act, first, self.ff, ops.GEMM_SWIGLU, self.w_up, st=self.rt.tc)
+        ops_tensor.gemm_runs(act, self.w_down, y, first, self.hidden, ops.GEMM_STORE, st=self.rt.tc)
         ops.experts_combine(y, h, chosen, weight, where, n, self.n_experts, self.top, x)
 
     def _shared(self, ctx, h, x, scale):

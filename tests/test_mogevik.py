@@ -548,7 +548,7 @@ def test_router_and_experts_both_ways(dtype, experts, identity, top, groups, kee
         act = torch.empty(T * top, ff, device="cuda", dtype=dtype)
         scratch = None
         if way == "expert":
-            scratch = (torch.full((experts + 1,), -1, dtype=torch.int32, device="cuda"),
+            scratch = (torch.full((2 * (experts + 1),), -1, dtype=torch.int32, device="cuda"),
                        torch.full((T * top,), -1, dtype=torch.int32, device="cuda"),
                        torch.full((T * top * W,), float("nan"), device="cuda"))
         ops.experts(_dev(h, dtype), stack("gate"), stack("up"), stack("down"), chosen, weight, T, experts, top, ff, act, x, scratch)
