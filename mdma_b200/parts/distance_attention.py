@@ -18,8 +18,8 @@ kernel for long steps, the mma.sync kernel between, the decode kernel for single
 kernels as the other attention mixers, with the slopes as one more per-head parameter); the gate is
 then a small kernel of its own.  Other geometries run on this mixer's CUDA-core kernels, which take
 keys and values of different sizes and apply the gate themselves: one that stages a tile's keys and
-values in shared memory for steps of many tokens, and one that keeps a warp per (token, head) and
-visits keys in position order (single tokens, and everything in the 32-bit engine).
+values in shared memory (the serving engine), and one that keeps a warp per (token, head) and visits
+keys in position order (the 32-bit engine, and geometries whose tile does not fit shared memory).
 """
 from __future__ import annotations
 
@@ -37,7 +37,6 @@ from .linear import Linear
 class DistanceAttention(Part):
     graph_safe = True      # forward reads no host-side per-step values
     MAX_HEAD_DIM = 256     # the kernels' limit for keys and for values
-    TILED_FROM = 8         # rows in the step's longest sequence from which the tiled kernel is used
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -146,7 +145,9 @@ class DistanceAttention(Part):
                 ops.sigmoid_gate(out, gate, n)
             self.o.accumulate(out, x, n, defer=False)
             return
-        tiled = self._tiled_ok and ctx.max_new >= self.TILED_FROM and qkv.dtype != torch.float32
+        # the serving engine stages keys and values per tile (also for single tokens: a block per sequence and kv head
+        # reads them once for the whole group); the 32-bit engine visits keys in position order, one warp per (token, head)
+        tiled = self._tiled_ok and qkv.dtype != torch.float32
         ops.attention_distance(qkv, view.k, view.v, ctx, view.page_table, view.max_pages, view.page_size, self.slopes,
                                gate, out, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, self.window,
                                self.scale, tiled)
