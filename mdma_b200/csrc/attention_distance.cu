@@ -118,6 +118,21 @@ attention_distance_plain_kernel(const T* __restrict__ q, int q_row_stride, const
 // columns.  The running maximum, normaliser and sums of a pair live in shared memory between chunks.
 constexpr int kTileRows = 16, kChunkKeys = 64, kTileWarps = 8;
 
+// eight consecutive elements as floats by 16-byte loads (the address is 16-byte aligned)
+__device__ __forceinline__ void stage8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void stage8(const __nv_bfloat16* p, float* v) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kTileWarps * 32)
 attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_cache,
@@ -150,6 +165,7 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
     float* sl = sm + kTileRows * group;                    // [kTileRows * group] normaliser
     float* sp = sl + kTileRows * group;                    // [kTileWarps][kChunkKeys] a pair's weights of the chunk
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool vec_k = dim % 8 == 0 && ((uintptr_t)k_cache & 15) == 0, vec_v = v_dim % 8 == 0 && ((uintptr_t)v_cache & 15) == 0;
 
     for (int e = threadIdx.x; e < pairs * dim; e += blockDim.x) {
         const int pr = e / dim, d = e % dim;
@@ -162,15 +178,37 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
     for (int c0 = first; c0 <= last; c0 += kChunkKeys) {
         const int n_keys = min(kChunkKeys, last + 1 - c0);
         __syncthreads();                                   // the chunk before is done with (and q is in place)
-        for (int e = threadIdx.x; e < n_keys * dim; e += blockDim.x) {
-            const int j = e / dim, d = e % dim, p = c0 + j;
-            const size_t row = ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh;
-            sk[j * kd + d] = to_float(k_cache[row * dim + d]);
-        }
-        for (int e = threadIdx.x; e < n_keys * v_dim; e += blockDim.x) {
-            const int j = e / v_dim, d = e % v_dim, p = c0 + j;
-            const size_t row = ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh;
-            sv[j * v_dim + d] = to_float(v_cache[row * v_dim + d]);
+        {   // four threads a key: one look at the page table, then 16-byte loads where the rows allow them
+            constexpr int kPerKey = kTileWarps * 32 / kChunkKeys;
+            const int j = threadIdx.x / kPerKey, part = threadIdx.x % kPerKey;
+            if (j < n_keys) {
+                const int p = c0 + j;
+                const size_t row = ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh;
+                const T* kp = k_cache + row * dim;
+                const T* vp = v_cache + row * v_dim;
+                float* kd_row = sk + j * kd;
+                float* vd_row = sv + j * v_dim;
+                if (vec_k) {
+                    for (int d = part * 8; d < dim; d += kPerKey * 8) {
+                        float t8[8];
+                        stage8(kp + d, t8);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) kd_row[d + i] = t8[i];
+                    }
+                } else {
+                    for (int d = part; d < dim; d += kPerKey) kd_row[d] = to_float(kp[d]);
+                }
+                if (vec_v) {
+                    for (int d = part * 8; d < v_dim; d += kPerKey * 8) {
+                        float t8[8];
+                        stage8(vp + d, t8);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) vd_row[d + i] = t8[i];
+                    }
+                } else {
+                    for (int d = part; d < v_dim; d += kPerKey) vd_row[d] = to_float(vp[d]);
+                }
+            }
         }
         __syncthreads();
         float* wp = sp + warp * kChunkKeys;

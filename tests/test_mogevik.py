@@ -483,6 +483,39 @@ def test_tensor_core_attention_with_a_distance_penalty(H, G, D, window, impl):
         assert (want[T - 1, 0] - v[edge, 0]).abs().max() > 0.2 * v[edge, 0].abs().max()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("features,K", [(64, 40), (96, 128), (256, 512)])
+def test_products_over_runs_of_rows(features, K):
+    """One library call runs a product per run of rows with the run's own matrix of a stack (stored and gated), on side
+    streams that join the caller's: runs of 0, 1, 3, 130 and 300 rows, against float products of the same bfloat16 values;
+    rows beyond the last run stay untouched."""
+    from mdma_b200 import ops, ops_tensor
+    g = torch.Generator().manual_seed(features + K)
+    lengths = [3, 0, 130, 1, 300, 0, 17]
+    first = [0]
+    for n in lengths:
+        first.append(first[-1] + n)
+    R, total = len(lengths), first[-1]
+    a = torch.randn(total + 5, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(R * features, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    w2 = (torch.randn(R * features, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    for gated in (False, True):
+        out = torch.full((total + 5, features), 7.0, device="cuda", dtype=torch.float32 if not gated else torch.bfloat16)
+        ops_tensor.gemm_runs(a.cuda(), w.cuda(), out, first, features, ops.GEMM_SWIGLU if gated else ops.GEMM_STORE,
+                             w2.cuda() if gated else None)
+        ops_tensor.check_status(out.device)
+        got = out.double().cpu()
+        for r in range(R):
+            rows = a[first[r]:first[r + 1]].double()
+            want = rows @ w[r * features:(r + 1) * features].double().T
+            if gated:
+                want = want * torch.sigmoid(want) * (rows @ w2[r * features:(r + 1) * features].double().T)
+            if len(rows):       # the gated result is rounded to bfloat16 on its way out
+                tol = (1e-2 * max(1.0, float(want.abs().max()))) if gated else 1e-3
+                assert (got[first[r]:first[r + 1]] - want).abs().max() < tol, (r, gated)
+        assert (got[total:] == 7.0).all()
+
+
 def _router_case(g, T, W, experts, identity, top, groups, keep, shared):
     n = experts + identity
     cfg = {"experts": experts, "identity": identity, "top": top}
