@@ -82,6 +82,9 @@ def distance_attention(h, W, p, sizes, slope_power=8.0):
     return (out.reshape(T, H * V) * torch.sigmoid(h @ W[p + "g"].T)) @ W[p + "o"].T
 
 
+_margins = None      # while a list: every call of `route` appends, per token, how close its choice was (see `forward`)
+
+
 def route(h, W, p, router):
     """(chosen [T, top], weights [T, top], scores s [T, n]) of the router."""
     n = router["experts"] + (router.get("identity") or 0)
@@ -97,8 +100,18 @@ def route(h, W, p, router):
                 if g not in kept:
                     c[t, g * per:(g + 1) * per] = float("-inf")
     chosen = torch.empty(h.shape[0], router["top"], dtype=torch.long)
+    margin = torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
     for t in range(h.shape[0]):
-        chosen[t] = torch.tensor(sorted(range(n), key=lambda e: (-float(c[t, e]), e))[:router["top"]])
+        order = sorted(range(n), key=lambda e: (-float(c[t, e]), e))
+        chosen[t] = torch.tensor(order[:router["top"]])
+        if router["top"] < n and float(c[t, order[router["top"]]]) > float("-inf"):
+            margin[t] = c[t, order[router["top"] - 1]] - c[t, order[router["top"]]]      # last chosen against first left out
+    if groups and groups["keep"] < groups["count"]:
+        per = n // groups["count"]
+        gs = (s + W[p + "correction"]).view(-1, groups["count"], per).max(-1).values.sort(-1, descending=True).values
+        margin = torch.minimum(margin, gs[:, groups["keep"] - 1] - gs[:, groups["keep"]])   # last kept group against the next
+    if _margins is not None:
+        _margins.append(margin)
     picked = s.gather(1, chosen)
     return chosen, picked / (picked.sum(-1, keepdim=True) + 1e-20), s
 
@@ -133,10 +146,14 @@ def schedule(cfg):
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(cfg, tensors, ids, trace=None, skip=None):
+def forward(cfg, tensors, ids, trace=None, skip=None, margins=None):
     """Logits [T, vocab] of one sequence.  `trace`: a list that receives the residual stream after every run of a
-    layer.  `skip`: the name of one mechanism to leave out (tests use it to show that each one matters)."""
+    layer.  `skip`: the name of one mechanism to leave out (tests use it to show that each one matters).  `margins`: a
+    list that receives ONE tensor [T]: per token, the smallest distance by which any router of any run decided (between
+    the last expert chosen and the first left out, and between the last group kept and the next)."""
+    global _margins
     W = {k: v.to(F64) for k, v in tensors.items()}
+    _margins = [] if margins is not None else None
     eps = cfg["norm"]["eps"]
     x = W["embed"][torch.tensor(ids)] * (1.0 if skip == "embedding_scale" else (cfg.get("embedding") or {}).get("scale", 1.0))
     x0 = x.clone()
@@ -166,4 +183,7 @@ def forward(cfg, tensors, ids, trace=None, skip=None):
         x = x + (mix + ff)
         if trace is not None:
             trace.append(x.clone())
+    if margins is not None:
+        margins.append(torch.stack(_margins).min(0).values if _margins else torch.full((len(ids),), float("inf"), dtype=F64))
+    _margins = None
     return layer_norm(x, W["final.norm"], eps) @ W["embed"].T

@@ -867,7 +867,7 @@ def random_config(seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("seed", range(12))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("MOGEVIK_DRAWN_CONFIGS", "12"))))
 def test_random_configurations(seed):
     """Drawn configurations in both engines: two unequal prompts in one step, six tokens decoded, against the plain
     statement; pages of 16 or 64 rows."""
@@ -879,17 +879,123 @@ def test_random_configurations(seed):
     seqs = [ids_of(cfg, n + 6, 90 + seed + i) for i, n in enumerate(lengths)]
     for dtype, store in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
         d, W = make_model(cfg, 200 + seed, store)
-        refs = [pm.forward(cfg, W, s).numpy() for s in seqs]
+        refs, sure = [], []
+        for s in seqs:
+            m = []
+            refs.append(pm.forward(cfg, W, s, margins=m).numpy())
+            sure.append(_rows_before_a_close_call(m[0]) if dtype == "bfloat16" else len(s))
         eng = Engine(d, dtype=dtype, max_batch=2, max_context=192, logit_rows=192, page_size=r.choice([16, 64]))
         slots = [eng.acquire(), eng.acquire()]
         eng.cache.poison_unused()
         out = eng.step([StepEntry(sl, s[:n], list(range(n))) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
-        close(out[:lengths[0]], refs[0][:lengths[0]], dtype, f"{cfg}: first prompt", drawn=True)
-        close(out[lengths[0]:], refs[1][:lengths[1]], dtype, f"{cfg}: second prompt", drawn=True)
+        assert np.isfinite(out).all()
+        close_drawn(out[:lengths[0]], refs[0][:lengths[0]], dtype, f"{cfg}: first prompt", range(lengths[0]), sure[0])
+        close_drawn(out[lengths[0]:], refs[1][:lengths[1]], dtype, f"{cfg}: second prompt", range(lengths[1]), sure[1])
         for p in range(6):
             eng.cache.poison_unused()
             out = eng.step([StepEntry(sl, [s[n + p]], [0]) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
-            close(out, np.stack([refs[0][lengths[0] + p], refs[1][lengths[1] + p]]), dtype, f"{cfg}: decoded {p}", drawn=True)
+            assert np.isfinite(out).all()
+            for i in range(2):
+                close_drawn(out[i], refs[i][lengths[i] + p], dtype, f"{cfg}: decoded {p}", [lengths[i] + p], sure[i])
+        eng.check_status()
+        del eng
+
+
+def close_drawn(got, ref, dtype, what, positions, sure):
+    """All rows against the plain statement; in bfloat16, if that fails, the rows that come before the sequence's first
+    close routing call must still agree (`positions`: each row's place in its sequence; `sure`: how many places come
+    before that call).  A difference in a row that no close call precedes is a fault; one behind such a call need not be."""
+    got, ref = np.atleast_2d(got), np.atleast_2d(ref)
+    try:
+        close(got, ref, dtype, what, drawn=True)
+    except AssertionError:
+        keep = [j for j, p in enumerate(positions) if p < sure]
+        if dtype == "float32" or len(keep) == len(positions):
+            raise
+        if keep:
+            close(got[keep], ref[keep], dtype, what + " (rows before a close routing call)", drawn=True)
+
+
+def _rows_before_a_close_call(margin, closer_than=5e-3):
+    """How many rows of a sequence come before the first token whose routing was decided by less than `closer_than`.
+    In bfloat16 such a token may take another expert than in the float64 statement; a recurrent state or a later
+    attention then carries the difference to every later row, so only the rows before it can be compared row by row
+    (the float32 engine is compared on all rows)."""
+    near = torch.nonzero(margin < closer_than).view(-1)
+    return int(near[0]) if len(near) else len(margin)
+
+
+def larger_config(seed):
+    """Sizes of a small real model: widths of a few hundred, up to sixteen heads of 32 to 128, value heads of another
+    size or the same, windows of 50 to 300 or none, eight to thirty-two experts in groups, three to five layers with a loop."""
+    import random
+    r = random.Random(5000 + seed)
+    width = r.choice([256, 320, 384, 512])
+    n = r.randint(3, 5)
+    layers = []
+    for _ in range(n):
+        if r.random() < 0.5:
+            blocks = r.choice([2, 4, 8])
+            kind, mixer = "rglru", {"width": blocks * r.choice([40, 64, 80, 96]), "blocks": blocks, "conv": r.choice([2, 4])}
+        else:
+            heads = r.choice([4, 8, 12, 16])
+            dim = r.choice([32, 64, 96, 128])
+            kind, mixer = "attention", {"heads": heads, "kv_heads": r.choice([g for g in (1, 2, 4, heads) if heads % g == 0]),
+                                        "dim": dim, "vdim": r.choice([dim, dim, dim // 2, 48, 64, 128]), "scale": round(dim ** -0.5, 4),
+                                        "mask": r.choice([None, {"size": r.choice([50, 72, 128, 200, 300])}])}
+        count = r.choice([2, 4, 8])
+        per = r.choice([2, 3, 4])
+        total = count * per
+        identity = r.choice([0, per, 2 * per]) if total > 2 * per else 0
+        keep = r.randint(max(1, count // 2), count)
+        router = {"experts": total - identity, "identity": identity, "top": r.randint(2, min(6, keep * per)),
+                  "groups": {"count": count, "keep": keep}}
+        layers.append({"type": kind, "mixer": mixer,
+                       "mlp": {"kind": "moe", "expert": {"ff": r.choice([64, 96, 128, 200])}, "router": router,
+                               "shared": {"ff": r.choice([128, 192, 256])}}})
+    start = r.randint(0, n - 2)
+    return {"architecture": "Mogevik", "vocab": r.randint(500, 1500), "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": round(width ** 0.5, 3)}, "layers": layers,
+            "loop": {"start": start, "stop": r.randint(start + 1, n), "times": r.randint(1, 3)}}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(int(os.environ.get("MOGEVIK_LARGER_CONFIGS", "3"))))
+def test_larger_random_configurations(seed):
+    """Drawn configurations of a small real model's sizes in both engines: a prompt of 700 tokens beside one of 90 in one
+    step (rows near the start, around every window's length and at the end are compared), then eight tokens decoded."""
+    from mdma_b200.engine import Engine, StepEntry
+    cfg = larger_config(seed)
+    lengths = [700, 90]
+    seqs = [ids_of(cfg, n + 8, 300 + seed + i) for i, n in enumerate(lengths)]
+    want = [sorted({0, 1, 2, 49, 50, 51, 71, 72, 73, 127, 128, 129, 199, 200, 201, 299, 300, 301, 511, 512, 698, 699}),
+            [0, 1, 49, 50, 71, 72, 89]]
+    for dtype, store in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        d, W = make_model(cfg, 700 + seed, store)
+        refs, sure = [], []
+        for s in seqs:
+            m = []
+            refs.append(pm.forward(cfg, W, s, margins=m).numpy())
+            sure.append(_rows_before_a_close_call(m[0]) if dtype == "bfloat16" else len(s))
+        eng = Engine(d, dtype=dtype, max_batch=2, max_context=768, logit_rows=64)
+        slots = [eng.acquire(), eng.acquire()]
+        eng.cache.poison_unused()
+        out = eng.step([StepEntry(sl, s[:n], w) for sl, s, n, w in zip(slots, seqs, lengths, want)]).cpu().numpy()
+        assert np.isfinite(out).all()
+        o = 0
+        for i in range(2):
+            close_drawn(out[o:o + len(want[i])], refs[i][want[i]], dtype, f"{cfg}: prompt {i}", want[i], sure[i])
+            o += len(want[i])
+        rows = [[], []]
+        for p in range(8):
+            eng.cache.poison_unused()
+            step_out = eng.step([StepEntry(sl, [s[n + p]], [0]) for sl, s, n in zip(slots, seqs, lengths)]).cpu().numpy()
+            assert np.isfinite(step_out).all()
+            for i in range(2):
+                rows[i].append(step_out[i].copy())
+        for i in range(2):
+            places = list(range(lengths[i], lengths[i] + 8))
+            close_drawn(np.stack(rows[i]), refs[i][places], dtype, f"{cfg}: decoded, sequence {i}", places, sure[i])
         eng.check_status()
         del eng
 
