@@ -806,6 +806,31 @@ def test_greedy_generation_through_the_scheduler(key):
 
 
 @pytest.mark.gpu
+def test_forty_sequences_decoded_together_replayed_and_step_by_step():
+    """More sequences than the token-by-token expert kernels take in one step: a decode step of forty sorts its pairs by
+    expert on the device, also inside a replayed graph.  Replayed and step-by-step runs give the same tokens, and the
+    float32 tokens are the plain statement's greedy continuation for the requests that are checked."""
+    from mdma_b200.engine import Engine
+    d, cfg, W = model_of("A", "float32")
+    prompts = [ids_of(cfg, 3 + (7 * i) % 23, 400 + i) for i in range(40)]
+    eng = Engine(d, dtype="float32", max_batch=40, max_context=48)
+    a = eng.generate(prompts, max_tokens=6, use_graphs=True)
+    b = eng.generate(prompts, max_tokens=6, use_graphs=False)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
+    for i in (0, 17, 39):
+        ids = list(prompts[i])
+        for _ in range(6):
+            ids.append(int(pm.forward(cfg, W, ids)[-1].argmax()))
+        assert a[i].tokens == ids[len(prompts[i]):], i
+    d16, _, _ = model_of("A", "bfloat16")
+    eng = Engine(d16, dtype="bfloat16", max_batch=40, max_context=48)
+    a = eng.generate(prompts, max_tokens=6, use_graphs=True)
+    b = eng.generate(prompts, max_tokens=6, use_graphs=False)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
+    eng.cache.check()
+
+
+@pytest.mark.gpu
 def test_trace_replay_and_command_line(tmp_path):
     from replay_util import replay
     d, cfg, W = model_of("B", "float32")
