@@ -112,11 +112,12 @@ attention_distance_plain_kernel(const T* __restrict__ q, int q_row_stride, const
 // Block = (tile of kTileRows query rows of one sequence, kv head).  The keys a tile can see are
 // [first key of its first row, position of its last row]; they are walked in chunks of kChunkKeys keys
 // that are staged in shared memory as float (keys [chunk][dim + 1], values [chunk][v_dim]).  Each warp
-// owns (row, head) pairs of the tile in turn; for a pair, a lane takes the keys lane, lane + 32, ... of
-// the chunk: it computes whole scores from shared memory (no shuffles per key), the warp agrees on the
-// chunk's maximum, and the weighted sum over the chunk's values is taken with lanes over the value
-// columns.  The running maximum, normaliser and sums of a pair live in shared memory between chunks.
-constexpr int kTileRows = 16, kChunkKeys = 64, kTileWarps = 8;
+// owns rows of the tile in turn, with up to four of the group's heads at once; a lane takes the keys lane,
+// lane + 32, ... of the chunk: it computes whole scores from shared memory (no shuffles per key; a key's
+// numbers are read once for the heads together), the warp agrees on each head's maximum of the chunk, and
+// the weighted sums over the chunk's values are taken with lanes over the value columns.  The running
+// maximum, normaliser and sums of a (row, head) pair live in shared memory between chunks.
+constexpr int kTileRows = 16, kChunkKeys = 64, kTileWarps = 8, kHeadsTogether = 4;
 
 // eight consecutive elements as floats by 16-byte loads (the address is 16-byte aligned)
 __device__ __forceinline__ void stage8(const float* p, float* v) {
@@ -133,7 +134,9 @@ __device__ __forceinline__ void stage8(const __nv_bfloat16* p, float* v) {
     }
 }
 
-template <typename T>
+// GH: how many of a group's heads a warp takes together (4, or 1 for steps whose tiles have a row or two: there the
+// warps would be left without work).
+template <typename T, int GH>
 __global__ void __launch_bounds__(kTileWarps * 32)
 attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_cache,
                                 const T* __restrict__ v_cache, const int* __restrict__ seq_start,
@@ -163,7 +166,7 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
     float* so = sv + (size_t)kChunkKeys * v_dim;           // [kTileRows * group][v_dim]
     float* sm = so + (size_t)kTileRows * group * v_dim;    // [kTileRows * group] running maximum
     float* sl = sm + kTileRows * group;                    // [kTileRows * group] normaliser
-    float* sp = sl + kTileRows * group;                    // [kTileWarps][kChunkKeys] a pair's weights of the chunk
+    float* sp = sl + kTileRows * group;                    // [kTileWarps][kHeadsTogether][kChunkKeys] weights of the chunk
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool vec_k = dim % 8 == 0 && ((uintptr_t)k_cache & 15) == 0, vec_v = v_dim % 8 == 0 && ((uintptr_t)v_cache & 15) == 0;
 
@@ -211,50 +214,85 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
             }
         }
         __syncthreads();
-        float* wp = sp + warp * kChunkKeys;
-        for (int pr = warp; pr < pairs; pr += kTileWarps) {
-            const int r = pr / group, g = pr % group;
+        // a warp takes a row and up to kHeadsTogether of the group's heads at once: a key's numbers (and later a
+        // value's) are read from shared memory once for all of them
+        float* wp = sp + warp * kHeadsTogether * kChunkKeys;
+        const int head_chunks = (group + GH - 1) / GH;
+        for (int unit = warp; unit < rows * head_chunks; unit += kTileWarps) {
+            const int r = unit / head_chunks, g0 = (unit % head_chunks) * GH;
+            const int ng = min(GH, group - g0);
+            const int pr0 = r * group + g0;
             const int pos = pos0 + r;
             const int lo = window > 0 ? max(0, pos + 1 - window) : 0;
-            const float slope = slopes ? slopes[kvh * group + g] : 0.f;
-            const float* qp = sq + (size_t)pr * dim;
-            float sc[kChunkKeys / 32];
-            float cmax = -INFINITY;
+            const float* qp = sq + (size_t)pr0 * dim;
+            float sc[kChunkKeys / 32][GH];
+            float cmax[GH];
+#pragma unroll
+            for (int g = 0; g < GH; ++g) cmax[g] = -INFINITY;
 #pragma unroll
             for (int u = 0; u < kChunkKeys / 32; ++u) {
                 const int j = lane + 32 * u, p = c0 + j;
-                float dot = -INFINITY;
-                if (j < n_keys && p <= pos && p >= lo) {
-                    const float* kp = sk + j * kd;
-                    float a = 0.f;
-                    for (int d = 0; d < dim; ++d) a = fmaf(qp[d], kp[d], a);
-                    dot = a * scale - slope * (float)(pos - p);
-                }
-                sc[u] = dot;
-                cmax = fmaxf(cmax, dot);
-            }
-            cmax = warp_max(cmax);
-            if (cmax == -INFINITY) continue;               // none of the chunk's keys is visible to this row
-            const float m_old = sm[pr];
-            const float m_new = fmaxf(m_old, cmax);
-            const float corr = expf(m_old - m_new);
-            float lsum = 0.f;
+                const bool seen = j < n_keys && p <= pos && p >= lo;
+                float a[GH];
 #pragma unroll
-            for (int u = 0; u < kChunkKeys / 32; ++u) {
-                const float pe = sc[u] == -INFINITY ? 0.f : expf(sc[u] - m_new);
-                wp[lane + 32 * u] = pe;
-                lsum += pe;
+                for (int g = 0; g < GH; ++g) a[g] = 0.f;
+                if (seen) {
+                    const float* kp = sk + j * kd;
+                    for (int d = 0; d < dim; ++d) {
+                        const float kv = kp[d];
+#pragma unroll
+                        for (int g = 0; g < GH; ++g)
+                            if (g < ng) a[g] = fmaf(qp[(size_t)g * dim + d], kv, a[g]);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < GH; ++g) {
+                    const float slope = (slopes && g < ng) ? slopes[kvh * group + g0 + g] : 0.f;
+                    sc[u][g] = (seen && g < ng) ? a[g] * scale - slope * (float)(pos - p) : -INFINITY;
+                    cmax[g] = fmaxf(cmax[g], sc[u][g]);
+                }
             }
-            lsum = warp_sum(lsum);
+            float corr[GH], lsum[GH], m_new[GH];
+            bool any = false;
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                cmax[g] = warp_max(cmax[g]);
+                const bool live = cmax[g] != -INFINITY;        // else none of the chunk's keys is visible to this row and head
+                any = any || live;
+                const float m_old = (g < ng) ? sm[pr0 + g] : -INFINITY;
+                m_new[g] = live ? fmaxf(m_old, cmax[g]) : m_old;
+                corr[g] = live ? expf(m_old - m_new[g]) : 1.f;
+                float part = 0.f;
+#pragma unroll
+                for (int u = 0; u < kChunkKeys / 32; ++u) {
+                    const float pe = (!live || sc[u][g] == -INFINITY) ? 0.f : expf(sc[u][g] - m_new[g]);
+                    wp[g * kChunkKeys + lane + 32 * u] = pe;
+                    part += pe;
+                }
+                lsum[g] = warp_sum(part);
+            }
+            if (!any) continue;
             __syncwarp();
-            float* op = so + (size_t)pr * v_dim;
+            float* op = so + (size_t)pr0 * v_dim;
             for (int d = lane; d < v_dim; d += 32) {
-                float a = op[d] * corr;
-                for (int j = 0; j < n_keys; ++j) a = fmaf(wp[j], sv[j * v_dim + d], a);
-                op[d] = a;
+                float a[GH];
+#pragma unroll
+                for (int g = 0; g < GH; ++g) a[g] = (g < ng) ? op[(size_t)g * v_dim + d] * corr[g] : 0.f;
+                for (int j = 0; j < n_keys; ++j) {
+                    const float v = sv[j * v_dim + d];
+#pragma unroll
+                    for (int g = 0; g < GH; ++g) a[g] = fmaf(wp[g * kChunkKeys + j], v, a[g]);
+                }
+#pragma unroll
+                for (int g = 0; g < GH; ++g)
+                    if (g < ng) op[(size_t)g * v_dim + d] = a[g];
             }
             __syncwarp();
-            if (lane == 0) { sm[pr] = m_new; sl[pr] = sl[pr] * corr + lsum; }
+            if (lane == 0) {
+#pragma unroll
+                for (int g = 0; g < GH; ++g)
+                    if (g < ng) { sm[pr0 + g] = m_new[g]; sl[pr0 + g] = sl[pr0 + g] * corr[g] + lsum[g]; }
+            }
         }
     }
     __syncthreads();
@@ -272,7 +310,7 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
 static size_t tiled_smem_bytes(int group, int dim, int v_dim) {
     const size_t pairs = (size_t)kTileRows * group;
     return sizeof(float) * (pairs * dim + (size_t)kChunkKeys * (dim + 1) + (size_t)kChunkKeys * v_dim + pairs * v_dim +
-                            2 * pairs + (size_t)kTileWarps * kChunkKeys);
+                            2 * pairs + (size_t)kTileWarps * kHeadsTogether * kChunkKeys);
 }
 
 }  // namespace mdma
@@ -317,17 +355,25 @@ int mdma_attention_distance(const void* q, int dtype, int q_row_stride, const vo
         MDMA_REQUIRE(smem <= 200 * 1024, "attention: the tiled kernel's shared memory (%zu bytes) does not fit", smem);
         MDMA_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv_heads <= 65535 && max_new > 0, "attention: bad batch");
         dim3 grid((max_new + kTileRows - 1) / kTileRows, n_kv_heads, n_seqs);
+        const int tile_rows = max_new < kTileRows ? max_new : kTileRows;
+        const bool together = tile_rows * ((group + kHeadsTogether - 1) / kHeadsTogether) >= kTileWarps;
+#define MDMA_TILED_LAUNCH(GH)                                                                                              \
+        do {                                                                                                                \
+            static bool raised = false;                                                                                     \
+            if (!raised) {                                                                                                  \
+                cudaFuncSetAttribute(attention_distance_tiled_kernel<T, GH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+                raised = true;                                                                                              \
+            }                                                                                                               \
+            launch_chained(attention_distance_tiled_kernel<T, GH>, grid, dim3(kTileWarps * 32), smem, stream, (const T*)q,  \
+                           q_row_stride, (const T*)k_cache, (const T*)v_cache, seq_start, seq_pos0, seq_slot, page_table,   \
+                           max_pages, page_size, slopes, (const T*)gate, gate_stride, (T*)out, n_heads, n_kv_heads, dim,    \
+                           v_dim, window, scale);                                                                           \
+        } while (0)
         MDMA_DISPATCH_DTYPE(dtype, T, {
-            static bool raised = false;
-            if (!raised) {
-                cudaFuncSetAttribute(attention_distance_tiled_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-                raised = true;
-            }
-            launch_chained(attention_distance_tiled_kernel<T>, grid, dim3(kTileWarps * 32), smem, stream, (const T*)q,
-                           q_row_stride, (const T*)k_cache, (const T*)v_cache, seq_start, seq_pos0, seq_slot, page_table,
-                           max_pages, page_size, slopes, (const T*)gate, gate_stride, (T*)out, n_heads, n_kv_heads, dim,
-                           v_dim, window, scale);
+            if (together) MDMA_TILED_LAUNCH(kHeadsTogether);
+            else MDMA_TILED_LAUNCH(1);
         });
+#undef MDMA_TILED_LAUNCH
         MDMA_LAUNCH_OK("attention_distance_tiled");
         return 0;
     }
