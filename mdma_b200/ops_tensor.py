@@ -227,11 +227,9 @@ def gemm_runs(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first: list, 
     assert w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype)
     st = st or _device_state(a.device)
     flush_pending(a.device, st)
-    most = max(first[r + 1] - first[r] for r in range(n_runs)) if n_runs else 0
-    if most == 0:
+    if first[-1] == first[0]:
         return
-    bn, splits = gemm_plan(mode, most, n_features, K, st.sms)
-    st.need(max(gemm_scratch_floats(bn, max(splits, 1), most, n_features, st.sms), 2 * st.sms * 128 * 64), "a K-split product")
+    # (the runs are launched in forms that need no scratch, so that they can run side by side: nothing to reserve)
     arr = (ctypes.c_int * (n_runs + 1))(*first)
     live = sum(1 for r in range(n_runs) if first[r + 1] > first[r])
     _call("tensor", "mdma_gemm_tc_runs", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), ctypes.c_long(n_features * K),
