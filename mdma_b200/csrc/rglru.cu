@@ -124,29 +124,44 @@ rglru_scan_runs_kernel(const LruRow in, const TW* __restrict__ rb, const TW* __r
 
 // ---------------------------------------------------------------- layer norm, weight only
 // y[r,:] = (x[src,:] - mean) / sqrt(var + eps) * w, var the mean of the squared deviations; src = rows[r] or r.
-// One block per row; the row is read three times (it stays in L1); sums in float, fixed order.
-template <typename TO, typename TW>
-__global__ void __launch_bounds__(256)
+// One block per row.  The row is read from memory once and kept in shared memory (STAGED) for the two further passes;
+// rows too long for that are read three times.  Sums in float, fixed order.
+template <typename TO, typename TW, bool STAGED>
+__global__ void __launch_bounds__(1024)
 layernorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, const int* __restrict__ rows,
                  TO* __restrict__ y, int width, float eps) {
     chain_release();
     chain_wait();
+    extern __shared__ __align__(16) float staged_row[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
     float sum = 0.f;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) sum += xr[e];
-    const float mean = block_sum(sum, scratch) / (float)width;
+    if (STAGED && width % 4 == 0 && ((uintptr_t)xr & 15) == 0) {
+        for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + e);
+            *reinterpret_cast<float4*>(staged_row + e) = v;
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+        for (int e = threadIdx.x; e < width; e += blockDim.x) {
+            const float v = xr[e];
+            if (STAGED) staged_row[e] = v;
+            sum += v;
+        }
+    }
+    const float* row = STAGED ? staged_row : xr;
+    const float mean = block_sum(sum, scratch) / (float)width;      // (its barriers also publish the staged row)
     float sq = 0.f;
     for (int e = threadIdx.x; e < width; e += blockDim.x) {
-        const float d = xr[e] - mean;
+        const float d = row[e] - mean;
         sq = fmaf(d, d, sq);
     }
     const float var = block_sum(sq, scratch) / (float)width;
     const float inv = 1.0f / sqrtf(var + eps);
     TO* yr = y + (size_t)r * width;
     for (int e = threadIdx.x; e < width; e += blockDim.x)
-        yr[e] = from_float<TO>((xr[e] - mean) * inv * to_float(w[e]));
+        yr[e] = from_float<TO>((row[e] - mean) * inv * to_float(w[e]));
 }
 
 // ---------------------------------------------------------------- re-entry of a looped stack by addition
@@ -222,10 +237,17 @@ int mdma_layernorm(const float* x, const void* w, int w_dtype, const int* rows, 
                    int width, float eps, cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes");
     if (n_rows == 0) return 0;
+    // 256 threads up to 2,048 columns, 1,024 beyond; the row staged while it fits 48 KB of shared memory
+    const int threads = width <= 2048 ? 256 : 1024;
+    const size_t staged = (size_t)width * sizeof(float);
     MDMA_DISPATCH_DTYPE(y_dtype, TO,
         MDMA_DISPATCH_DTYPE(w_dtype, TW,
-            launch_chained(layernorm_kernel<TO, TW>, dim3(n_rows), dim3(256), 0, stream, x, (const TW*)w, rows, (TO*)y,
-                           width, eps)));
+            if (staged <= 48 * 1024)
+                launch_chained(layernorm_kernel<TO, TW, true>, dim3(n_rows), dim3(threads), staged, stream, x, (const TW*)w, rows,
+                               (TO*)y, width, eps);
+            else
+                launch_chained(layernorm_kernel<TO, TW, false>, dim3(n_rows), dim3(threads), 0, stream, x, (const TW*)w, rows,
+                               (TO*)y, width, eps)));
     MDMA_LAUNCH_OK("layernorm");
     return 0;
 }
